@@ -1,0 +1,125 @@
+"""ctypes binding of libb200tri.so (the C ABI declared in include/b200tri.h).
+
+The structures below mirror the header field for field. Loading fails loudly:
+there is no fallback implementation behind these calls.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libb200tri.so"
+
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = range(6)
+
+
+class B200TriError(RuntimeError):
+    """A libb200tri entry point returned a non-zero status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libb200tri error {code}: {message}")
+        self.code = code
+
+
+class TrimulArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("incoming", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("mask", C.c_void_p),
+        ("norm_in_scale", C.c_void_p), ("norm_in_bias", C.c_void_p),
+        ("p_in", C.c_void_p), ("g_in", C.c_void_p),
+        ("norm_out_scale", C.c_void_p), ("norm_out_bias", C.c_void_p),
+        ("p_out", C.c_void_p), ("g_out", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TrimulProjectArgs(C.Structure):
+    _fields_ = [
+        ("n_outer", C.c_int32), ("n_inner", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("xs_outer", C.c_int64), ("xs_inner", C.c_int64),
+        ("mask", C.c_void_p), ("ms_outer", C.c_int64), ("ms_inner", C.c_int64),
+        ("norm_in_scale", C.c_void_p), ("norm_in_bias", C.c_void_p),
+        ("p_in", C.c_void_p), ("g_in", C.c_void_p),
+        ("a", C.c_void_p), ("b", C.c_void_p),
+        ("ld", C.c_int64), ("chan_stride", C.c_int64), ("block_stride", C.c_int64),
+        ("rows_per_block", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TrimulContractArgs(C.Structure):
+    _fields_ = [
+        ("n_i", C.c_int32), ("n_j", C.c_int32), ("n_k", C.c_int32), ("n_src", C.c_int32),
+        ("a", C.c_void_p), ("a_ld", C.c_int64), ("a_chan_stride", C.c_int64), ("a_src_stride", C.c_int64),
+        ("b", C.c_void_p), ("b_ld", C.c_int64), ("b_chan_stride", C.c_int64), ("b_src_stride", C.c_int64),
+        ("acc_in", C.c_void_p), ("out_f32", C.c_void_p), ("out_bf16", C.c_void_p),
+        ("out_ld", C.c_int64), ("out_chan_stride", C.c_int64),
+    ]
+
+
+class TrimulFinishArgs(C.Structure):
+    _fields_ = [
+        ("n_i", C.c_int32), ("n_j", C.c_int32), ("eps", C.c_float),
+        ("t", C.c_void_p), ("t_ld", C.c_int64), ("t_chan_stride", C.c_int64),
+        ("x", C.c_void_p), ("xs_i", C.c_int64), ("xs_j", C.c_int64),
+        ("norm_in_scale", C.c_void_p), ("norm_in_bias", C.c_void_p),
+        ("norm_out_scale", C.c_void_p), ("norm_out_bias", C.c_void_p),
+        ("p_out", C.c_void_p), ("g_out", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("os_i", C.c_int64), ("os_j", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/b200tri.h declares.
+SIGNATURES = {
+    "b200tri_version": (C.c_int, []),
+    "b200tri_last_error": (C.c_char_p, []),
+    "b200tri_device_status": (C.c_int, []),
+    "b200tri_trimul_workspace_bytes": (C.c_size_t, [C.c_int32]),
+    "b200tri_trimul_forward": (C.c_int, [C.POINTER(TrimulArgs), C.c_void_p]),
+    "b200tri_trimul_project_workspace_bytes": (C.c_size_t, []),
+    "b200tri_trimul_project": (C.c_int, [C.POINTER(TrimulProjectArgs), C.c_void_p]),
+    "b200tri_trimul_contract": (C.c_int, [C.POINTER(TrimulContractArgs), C.c_void_p]),
+    "b200tri_trimul_finish_workspace_bytes": (C.c_size_t, []),
+    "b200tri_trimul_finish": (C.c_int, [C.POINTER(TrimulFinishArgs), C.c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library (once) and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m foldjax_b200.build` "
+            "(needs nvcc); foldjax_b200 has no fallback implementation"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        msg = load().b200tri_last_error()
+        raise B200TriError(rc, msg.decode() if msg else "unknown error")
+
+
+def device_status() -> int:
+    """Synchronise and return the device status word (0 = fine); raises on timeout codes."""
+    st = load().b200tri_device_status()
+    if st != 0:
+        msg = load().b200tri_last_error()
+        raise B200TriError(ERR_TIMEOUT, msg.decode() if msg else f"device status {st}")
+    return st

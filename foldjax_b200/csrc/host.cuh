@@ -1,0 +1,68 @@
+// Host-side plumbing shared by the translation units of libb200tri: error
+// reporting, the device status word, TMA descriptor encoding (through the
+// driver entry point, so the library does not link libcuda and still loads on
+// a machine without a GPU), and the workspace carve-up helper.
+#pragma once
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b200tri.h"
+
+namespace b200 {
+
+// Thread-local message behind b200tri_last_error().
+void set_error(const char* fmt, ...);
+const char* get_error();
+
+// Address of this device's status word (global memory, zero = fine). Kernels
+// record a bounded-wait timeout there.
+int* device_status_word();
+
+#define B200_CUDA_OK(expr)                                                              \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess) {                                                            \
+      b200::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, \
+                      __LINE__);                                                        \
+      return B200TRI_ERR_CUDA;                                                          \
+    }                                                                                   \
+  } while (0)
+
+#define B200_REQUIRE(cond, code, ...) \
+  do {                                \
+    if (!(cond)) {                    \
+      b200::set_error(__VA_ARGS__);   \
+      return (code);                  \
+    }                                 \
+  } while (0)
+
+enum class Swz { None, B64, B128 };
+
+// Encode a tiled tensor map over `rank` dimensions (innermost first).
+// strides_bytes[i] is the byte stride of dimension i+1 (dimension 0 is dense).
+int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, Swz swz);
+
+// Carves aligned pieces out of a caller-provided workspace.
+struct Carver {
+  uint8_t* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<uint8_t*>(p)) {}
+  template <typename T>
+  T* take(size_t count, size_t align = 1024) {
+    off = (off + align - 1) / align * align;
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+  size_t total() const { return (off + 1023) / 1024 * 1024; }
+};
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+int sm_count();
+
+}  // namespace b200

@@ -1,0 +1,115 @@
+// Library runtime: error text, device status word, TMA descriptor encoding.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "host.cuh"
+
+namespace b200 {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* get_error() { return g_error; }
+
+// One status word per device that loads the library.
+__device__ int g_status_word = 0;
+
+int* device_status_word() {
+  constexpr int kMaxDev = 64;
+  static int* cache[kMaxDev] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    cache[dev] = static_cast<int*>(p);
+  }
+  return cache[dev];
+}
+
+int sm_count() {
+  constexpr int kMaxDev = 64;
+  static int cache[kMaxDev] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 148;
+  if (!cache[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, Swz swz) {
+  auto fn = encode_fn();
+  B200_REQUIRE(fn != nullptr, B200TRI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, B200TRI_ERR_INVALID,
+               "tensor base %p is not 16-byte aligned", base);
+  for (int i = 0; i + 1 < rank; ++i)
+    B200_REQUIRE((strides_bytes[i] & 15) == 0, B200TRI_ERR_INVALID,
+                 "tensor stride %d (%llu bytes) is not a multiple of 16", i,
+                 static_cast<unsigned long long>(strides_bytes[i]));
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUtensorMapSwizzle s = CU_TENSOR_MAP_SWIZZLE_NONE;
+  if (swz == Swz::B64) s = CU_TENSOR_MAP_SWIZZLE_64B;
+  if (swz == Swz::B128) s = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUresult r = fn(out, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides_bytes, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, s, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_REQUIRE(r == CUDA_SUCCESS, B200TRI_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return B200TRI_OK;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200tri_version(void) { return 100; }
+
+const char* b200tri_last_error(void) { return b200::get_error(); }
+
+int b200tri_device_status(void) {
+  int* w = b200::device_status_word();
+  if (!w) {
+    b200::set_error("no CUDA device is current");
+    return -1;
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    b200::set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  int v = 0;
+  if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    b200::set_error("a kernel gave up on a bounded device wait (role code %d)", v);
+  }
+  return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,126 @@
+"""Triangle multiplicative update on B200 - host side.
+
+Mirrors ``triangle_multiplication_forward`` of the reference
+(src/foldjax/models/boltz2/models/triangle/triangle.py:33-129): same argument
+names and meaning, same parameter mapping, same error text for a bad direction.
+The arithmetic runs in libb200tri (hand-written sm_100a kernels); nothing here
+falls back to another implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Mapping
+
+import numpy as np
+import torch
+
+from . import _device as dev
+from . import _lib
+
+C_Z = 128  # channel width the kernels are built for
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check_pair(x: torch.Tensor) -> tuple[torch.Tensor, bool]:
+    squeeze = False
+    if x.dim() == 3:
+        x = x.unsqueeze(0)
+        squeeze = True
+    if x.dim() != 4 or x.shape[1] != x.shape[2]:
+        raise ValueError(f"expected a pair tensor [B, N, N, C], got shape {tuple(x.shape)}")
+    if x.shape[-1] != C_Z:
+        raise ValueError(f"libb200tri is built for c_z = {C_Z}; got {x.shape[-1]} channels")
+    return x, squeeze
+
+
+def _leaf(params: Mapping, *path: str) -> torch.Tensor:
+    node: Any = params
+    for key in path:
+        node = node[key]
+    if not isinstance(node, torch.Tensor) or not node.is_cuda or node.dtype != torch.bfloat16:
+        node = dev.to_device(node, torch.bfloat16)
+    return node.contiguous()
+
+
+def triangle_multiplication_forward(
+    params: Mapping[str, Mapping[str, Any]],
+    x: Any,
+    mask: Any,
+    direction: str,
+    eps: float = 1e-5,
+    chunk_size: int = 128,
+    glu_backend: str = "xla",
+    contraction_precision: str = "float32",
+    *,
+    residual: Any | None = None,
+    out: torch.Tensor | None = None,
+):
+    """Boltz triangle multiplication, outgoing or incoming.
+
+    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``) in bf16, ``mask`` is
+    ``[B, N, N]`` or None. Device tensors in -> device tensor out; NumPy / CPU
+    tensors in -> the inputs are copied to the GPU, the result is copied back and
+    returned as the same kind of array (the end-to-end path).
+
+    ``chunk_size``, ``glu_backend`` and ``contraction_precision`` are accepted for
+    signature compatibility: a fused backend has nothing to chunk, and the
+    contraction always accumulates in fp32 on the tensor cores (the reference's
+    default "float32" mode).  ``residual`` (optional) fuses the caller's
+    ``z + update``.
+    """
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"Unsupported triangle multiplication direction: {direction!r}")
+    if contraction_precision not in ("float32", "bf16"):
+        raise ValueError(f"Unsupported contraction_precision: {contraction_precision!r}")
+    dev.require_cuda()
+    lib = _lib.load()
+    host_in = dev.is_host_array(x)
+    numpy_in = isinstance(x, np.ndarray)
+    xd, squeeze = _check_pair(dev.to_device(x, torch.bfloat16))
+    b, n = xd.shape[0], xd.shape[1]
+    md = None
+    if mask is not None:
+        md = dev.to_device(mask, torch.float32)
+        if md.dim() == 2:
+            md = md.unsqueeze(0)
+        if tuple(md.shape) != (b, n, n):
+            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
+    rd = None
+    if residual is not None:
+        rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+    if out is None:
+        out = torch.empty_like(xd)
+    else:
+        out, _ = _check_pair(out)
+    leaves = {
+        "norm_in_scale": _leaf(params, "norm_in", "scale"),
+        "norm_in_bias": _leaf(params, "norm_in", "bias"),
+        "p_in": _leaf(params, "p_in", "kernel"),
+        "g_in": _leaf(params, "g_in", "kernel"),
+        "norm_out_scale": _leaf(params, "norm_out", "scale"),
+        "norm_out_bias": _leaf(params, "norm_out", "bias"),
+        "p_out": _leaf(params, "p_out", "kernel"),
+        "g_out": _leaf(params, "g_out", "kernel"),
+    }
+    if tuple(leaves["p_in"].shape) != (C_Z, 2 * C_Z) or tuple(leaves["p_out"].shape) != (C_Z, C_Z):
+        raise ValueError("libb200tri is built for hidden width 128 (p_in [128,256], p_out [128,128])")
+    nbytes = lib.b200tri_trimul_workspace_bytes(n)
+    ws = dev.workspace(nbytes, "trimul")
+    for bi in range(b):
+        args = _lib.TrimulArgs(
+            n=n, incoming=int(direction == "incoming"), eps=float(eps),
+            x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
+            residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+            **{k: v.data_ptr() for k, v in leaves.items()},
+        )
+        _lib.check(lib.b200tri_trimul_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))
+    result = out[0] if squeeze else out
+    if host_in:
+        host = result.float().cpu() if numpy_in else result.cpu()
+        return host.numpy() if numpy_in else host
+    return result

@@ -1,0 +1,321 @@
+"""CPU oracle for the Pairformer triangle ops (NumPy).
+
+TEST INFRASTRUCTURE ONLY. Nothing in the product path imports this module; it
+is used by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline
+legs of ``bench.py`` as the checker, never as the thing shipped or measured as
+the product.
+
+It restates, in plain NumPy, the arithmetic of the reference's XLA (jnp) path
+(eightmm/FoldJAX; paths relative to its root):
+
+* layer norm ........... src/foldjax/models/boltz2/models/primitives/_common.py:15-26
+* sigmoid GLU .......... src/foldjax/models/boltz2/models/primitives/glu_backend.py:36-37
+* triangle multiplication  src/foldjax/models/boltz2/models/triangle/triangle.py:78-129, 227-241
+* triangle attention ... src/foldjax/models/boltz2/models/triangle/triangle_attention.py:125-162, 346-455
+
+The arithmetic itself lives in a dependency that is not vendored in the
+reference: jax / jaxlib 0.10.1 (uv.lock), i.e. XLA's dot, softmax, sigmoid and
+rsqrt. JAX is not installable here, so the jnp functions cannot be run.
+
+Pinning: the reference's own tests hold complete PyTorch restatements of both
+ops and assert its jnp path equals them to 2e-4 / 3e-4
+(tests/models/boltz2/test_triangle_checkpoint_parity.py:155-192,
+tests/models/boltz2/test_triangle_attention_checkpoint_parity.py:94-147).
+``tests/golden/make_golden.py`` imports those test helpers from the reference
+checkout and runs them on seeded inputs; the outputs are committed as
+``tests/golden/*.npz`` and ``tests/test_oracle.py`` holds this oracle to them.
+
+Two precisions are offered by every function:
+
+``dtype="float64"`` (or "float32")
+    every step in that precision, no intermediate rounding: the "truth".
+``dtype="bfloat16"``
+    the result the reference produces for bf16 inputs: fp32 statistics and
+    accumulation, with a round-to-bf16 at every point where the jnp code holds a
+    bf16 array (after each matmul, each elementwise op, the LN normalisation, the
+    q scaling, the attention output).
+"""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import numpy as np
+
+try:  # bf16 rounding in NumPy
+    import ml_dtypes
+
+    _BF16 = ml_dtypes.bfloat16
+except Exception:  # pragma: no cover - ml_dtypes ships with the image
+    _BF16 = None
+
+Params = Mapping[str, Mapping[str, np.ndarray]]
+
+
+# --------------------------------------------------------------------- helpers
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even to bf16, returned as float32."""
+    x = np.asarray(x, dtype=np.float32)
+    if _BF16 is not None:
+        return x.astype(_BF16).astype(np.float32)
+    u = x.view(np.uint32)
+    rounded = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return rounded.view(np.float32)
+
+
+class _Prec:
+    """Working precision plus the rounding applied where the reference holds the trunk dtype."""
+
+    def __init__(self, dtype: str):
+        if dtype not in ("float64", "float32", "bfloat16"):
+            raise ValueError(f"unsupported oracle dtype: {dtype!r}")
+        self.name = dtype
+        self.work = np.float64 if dtype == "float64" else np.float32
+        self.bf16 = dtype == "bfloat16"
+
+    def r(self, x: np.ndarray) -> np.ndarray:
+        return round_bf16(x) if self.bf16 else np.asarray(x, dtype=self.work)
+
+    def arr(self, x) -> np.ndarray:
+        return self.r(np.asarray(x, dtype=np.float32 if self.bf16 else self.work))
+
+
+def _sigmoid(x: np.ndarray) -> np.ndarray:
+    out = np.empty_like(x)
+    pos = x >= 0
+    out[pos] = 1.0 / (1.0 + np.exp(-x[pos]))
+    e = np.exp(x[~pos])
+    out[~pos] = e / (1.0 + e)
+    return out
+
+
+def layer_norm(x: np.ndarray, scale: np.ndarray, bias: np.ndarray, eps: float, dtype: str = "float64") -> np.ndarray:
+    """_common.py:15-26: fp32 statistics, biased variance, the normalised value
+    cast to the input dtype BEFORE the affine step, which runs in that dtype."""
+    pr = _Prec(dtype)
+    xf = pr.arr(x)
+    mean = xf.mean(axis=-1, keepdims=True, dtype=pr.work)
+    var = np.square(xf - mean).mean(axis=-1, keepdims=True, dtype=pr.work)
+    normed = pr.r((xf - mean) / np.sqrt(var + pr.work(eps)))
+    return pr.r(pr.r(normed * pr.arr(scale)) + pr.arr(bias))
+
+
+def _linear(x: np.ndarray, kernel: np.ndarray, pr: _Prec) -> np.ndarray:
+    """x @ kernel with the kernel in [in, out] layout; fp32 accumulate, output in the trunk dtype."""
+    return pr.r(np.matmul(x, pr.arr(kernel)))
+
+
+# ------------------------------------------------------- triangle multiplication
+def triangle_multiplication(
+    params: Params,
+    x: np.ndarray,
+    mask: np.ndarray | None,
+    direction: str,
+    eps: float = 1e-5,
+    dtype: str = "float64",
+) -> np.ndarray:
+    """triangle.py:78-129 (XLA path, contraction_precision="float32").
+
+    x [B,N,N,C], mask [B,N,N] -> update [B,N,N,C] (the caller adds the residual).
+    """
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"Unsupported triangle multiplication direction: {direction!r}")
+    pr = _Prec(dtype)
+    xn = layer_norm(x, params["norm_in"]["scale"], params["norm_in"]["bias"], eps, dtype)  # :78
+    x_in = xn
+    if mask is None:
+        mask = np.ones(xn.shape[:-1], dtype=pr.work)
+    m = pr.arr(mask)
+    gate = pr.r(_sigmoid(_linear(xn, params["g_in"]["kernel"], pr)))  # glu_backend.py:36-37
+    projected = pr.r(gate * _linear(xn, params["p_in"]["kernel"], pr))
+    projected = pr.r(projected * m[..., None])  # :90
+    a, b = np.split(projected.astype(pr.work), 2, axis=-1)  # :96-102, a = first half
+    if direction == "outgoing":
+        out = np.einsum("bikd,bjkd->bijd", a, b, optimize=True)  # :231
+    else:
+        out = np.einsum("bkid,bkjd->bijd", a, b, optimize=True)  # :239
+    out = pr.r(out)  # :124
+    out = layer_norm(out, params["norm_out"]["scale"], params["norm_out"]["bias"], eps, dtype)  # :126
+    out = _linear(out, params["p_out"]["kernel"], pr)  # :127
+    g = pr.r(_sigmoid(_linear(x_in, params["g_out"]["kernel"], pr)))  # :128
+    return pr.r(out * g)  # :129
+
+
+def triangle_contraction(a: np.ndarray, b: np.ndarray, direction: str) -> np.ndarray:
+    """triangle.py:227-241 on [N,N,C] operands, float64."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    if direction == "outgoing":
+        return np.einsum("ikd,jkd->ijd", a, b, optimize=True)
+    return np.einsum("kid,kjd->ijd", a, b, optimize=True)
+
+
+# ------------------------------------------------------------ triangle attention
+def attention_core(
+    q: np.ndarray,
+    k: np.ndarray,
+    v: np.ndarray,
+    tri_bias: np.ndarray,
+    mask_bias: np.ndarray,
+    dtype: str = "float64",
+    row_chunk: int = 16,
+) -> np.ndarray:
+    """triangle_attention.py:428-455.
+
+    q,k,v [B,I,H,J,D] (q pre-scaled); tri_bias [B,1,H,J,J]; mask_bias [B,I,1,1,J]
+    additive (0 / -inf constant). scores = (q k^T + mask_bias) + tri_bias in the
+    working precision, softmax, P v, cast to the trunk dtype. Rows are chunked
+    only to bound memory; rows are independent so the result is unchanged.
+    """
+    pr = _Prec(dtype)
+    work = pr.work
+    q = np.asarray(q, dtype=work)
+    k = np.asarray(k, dtype=work)
+    v = np.asarray(v, dtype=work)
+    tb = np.asarray(tri_bias, dtype=work)
+    mb = np.asarray(mask_bias, dtype=work)
+    out = np.empty_like(q)
+    n_i = q.shape[1]
+    for s in range(0, n_i, row_chunk):
+        e = min(n_i, s + row_chunk)
+        scores = np.matmul(q[:, s:e], np.swapaxes(k[:, s:e], -1, -2))
+        scores = scores + mb[:, s:e] + tb  # that order: :453
+        scores = scores - scores.max(axis=-1, keepdims=True)
+        p = np.exp(scores)
+        p /= p.sum(axis=-1, keepdims=True)
+        out[:, s:e] = np.matmul(p, v[:, s:e])
+    return pr.r(out)
+
+
+def triangle_attention(
+    params: Params,
+    x: np.ndarray,
+    mask: np.ndarray | None = None,
+    starting: bool = True,
+    inf: float = 1e9,
+    eps: float = 1e-5,
+    dtype: str = "float64",
+    return_parts: bool = False,
+):
+    """triangle_attention.py:79-162 and 346-425 (XLA path).
+
+    x [B,N,N,C], mask [B,N,N] -> update [B,N,N,C]. Heads come from the bias
+    projection's width, head dim from linear_g's.
+    """
+    pr = _Prec(dtype)
+    work = pr.work
+    xx = pr.arr(x)
+    if mask is None:
+        mask = np.ones(xx.shape[:-1], dtype=work)
+    m = np.asarray(mask, dtype=work)
+    if not starting:  # :128-130
+        xx = np.swapaxes(xx, -2, -3)
+        m = np.swapaxes(m, -1, -2)
+    xn = layer_norm(xx, params["layer_norm"]["scale"], params["layer_norm"]["bias"], eps, dtype)  # :132
+    # :138-142 - built in fp32 so the constant stays finite
+    mask_bias = (np.float32(inf) * (m.astype(np.float32) - np.float32(1.0)))[:, :, None, None, :]
+    tri_bias = _linear(xn, params["linear"]["kernel"], pr)  # [B,J,K,H]  :144
+    heads = tri_bias.shape[-1]
+    tri_bias = np.transpose(tri_bias, (0, 3, 1, 2))[:, None]  # [B,1,H,J,K]  :145-146
+
+    mha = params["mha"]
+    qg = _linear(xn, np.concatenate((mha["linear_q"]["kernel"], mha["linear_g"]["kernel"]), axis=-1), pr)  # :360
+    q, gate = np.split(qg, 2, axis=-1)
+    kv = _linear(xn, np.concatenate((mha["linear_k"]["kernel"], mha["linear_v"]["kernel"]), axis=-1), pr)  # :368
+    k, v = np.split(kv, 2, axis=-1)
+    c_hidden = np.asarray(mha["linear_g"]["kernel"]).shape[-1] // heads
+
+    def heads_first(t):  # [B,I,J,H*D] -> [B,I,H,J,D]   :377-382
+        t = t.reshape(t.shape[:-1] + (heads, c_hidden))
+        return np.swapaxes(t, -2, -3)
+
+    q, k, v = heads_first(q), heads_first(k), heads_first(v)
+    q_scale = pr.r(np.sqrt(np.asarray(c_hidden, dtype=work)))  # sqrt evaluated in the trunk dtype  :399
+    q = pr.r(q / q_scale)  # :400
+    o = attention_core(q, k, v, tri_bias, mask_bias, dtype)  # :414
+    o = np.swapaxes(o, -2, -3)  # [B,I,J,H,D]
+    g = pr.r(_sigmoid(gate)).reshape(gate.shape[:-1] + (heads, c_hidden))  # :421-422
+    o = pr.r(o * g)
+    o = o.reshape(o.shape[:-2] + (heads * c_hidden,))
+    out = _linear(o, mha["linear_o"]["kernel"], pr)  # :425
+    if not starting:  # :160-161
+        out = np.swapaxes(out, -2, -3)
+    if return_parts:
+        return out, {"q": q, "k": k, "v": v, "tri_bias": tri_bias, "mask_bias": mask_bias, "gate": g}
+    return out
+
+
+# ------------------------------------------------------------ synthetic inputs
+def random_trimul_params(rng: np.random.Generator, c_z: int = 128, c_hidden: int = 128, std: float = 0.02,
+                         ln_noise: float = 0.0) -> dict:
+    """Weights as the benchmark configs describe them: N(0, std^2) linear kernels
+    in [in, out] layout, layer-norm scale 1 / bias 0 (optionally perturbed so
+    that tests exercise the affine step)."""
+
+    def w(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    def ln(c):
+        return {
+            "scale": (1.0 + ln_noise * rng.standard_normal(c)).astype(np.float32),
+            "bias": (ln_noise * rng.standard_normal(c)).astype(np.float32),
+        }
+
+    return {
+        "norm_in": ln(c_z),
+        "p_in": {"kernel": w(c_z, 2 * c_hidden)},
+        "g_in": {"kernel": w(c_z, 2 * c_hidden)},
+        "norm_out": ln(c_hidden),
+        "p_out": {"kernel": w(c_hidden, c_z)},
+        "g_out": {"kernel": w(c_z, c_z)},
+    }
+
+
+def random_triatt_params(rng: np.random.Generator, c_z: int = 128, heads: int = 4, c_hidden: int = 32,
+                         std: float = 0.02, ln_noise: float = 0.0) -> dict:
+    def w(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    hd = heads * c_hidden
+    return {
+        "layer_norm": {
+            "scale": (1.0 + ln_noise * rng.standard_normal(c_z)).astype(np.float32),
+            "bias": (ln_noise * rng.standard_normal(c_z)).astype(np.float32),
+        },
+        "linear": {"kernel": w(c_z, heads)},
+        "mha": {
+            "linear_q": {"kernel": w(c_z, hd)},
+            "linear_k": {"kernel": w(c_z, hd)},
+            "linear_v": {"kernel": w(c_z, hd)},
+            "linear_g": {"kernel": w(c_z, hd)},
+            "linear_o": {"kernel": w(hd, c_z)},
+        },
+    }
+
+
+def round_params(params, dtype: str):
+    """Round every leaf to the trunk dtype (what a bf16 checkpoint cast does)."""
+    if dtype != "bfloat16":
+        return params
+    if isinstance(params, Mapping):
+        return {k: round_params(v, dtype) for k, v in params.items()}
+    return round_bf16(params)
+
+
+def pad_mask(n: int, n_pad: int) -> np.ndarray:
+    """pair mask m m^T with the last n_pad tokens dropped, shape [1, n, n]."""
+    m = np.ones(n, dtype=np.float32)
+    if n_pad:
+        m[n - n_pad:] = 0.0
+    return (m[:, None] * m[None, :])[None]
+
+
+def error_vs(ref: np.ndarray, got: np.ndarray) -> dict:
+    """The benchmark's error framing: max-abs and mean-abs error relative to the
+    RMS of the reference output (the reference's own scripts report the same,
+    tests/models/boltz2/scripts/compare_trunk_backends.py:25-40)."""
+    ref = np.asarray(ref, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(np.square(ref)))) or 1.0
+    diff = np.abs(ref - got)
+    return {"max_abs_over_rms": float(diff.max() / rms), "mean_abs_over_rms": float(diff.mean() / rms), "rms": rms}

@@ -1,0 +1,102 @@
+"""The oracle against the golden vectors produced by the reference's own
+PyTorch restatements (tests/golden/make_golden.py), plus the properties the
+reference's tests assert about these ops."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from conftest import load_triatt_golden, load_trimul_golden
+from oracle import triangle_oracle as orc
+
+
+@pytest.mark.parametrize("name", ["trimul_n7_c8.npz", "trimul_n12_c128.npz"])
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_trimul_matches_reference_restatement(name, direction):
+    params, x, mask, outs = load_trimul_golden(name)
+    got = orc.triangle_multiplication(params, x, mask, direction, dtype="float64")
+    # the reference accepts 2e-4 between its jnp path and this restatement
+    np.testing.assert_allclose(got, outs[direction], rtol=2e-4, atol=2e-4)
+    got32 = orc.triangle_multiplication(params, x, mask, direction, dtype="float32")
+    np.testing.assert_allclose(got32, outs[direction], rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("name", ["triatt_n7_c8.npz", "triatt_n12_c128.npz"])
+@pytest.mark.parametrize("starting", [True, False])
+def test_triatt_matches_reference_restatement(name, starting):
+    params, x, mask, outs = load_triatt_golden(name)
+    # Rows of the attention with no valid key hold "-1e9 absorbed in fp32" garbage
+    # in the reference (it depends on fp32 rounding of -1e9 + score), so they are
+    # compared in fp32 only; everything else also against the fp64 truth.
+    has_key = mask.any(axis=2) if starting else mask.any(axis=1)  # [B, N] per attention row
+    valid = has_key[:, :, None] if starting else has_key[:, None, :]
+    valid = np.broadcast_to(valid[..., None], outs[starting].shape)
+    got = orc.triangle_attention(params, x, mask, starting=starting, dtype="float64")
+    np.testing.assert_allclose(got[valid], outs[starting][valid], rtol=3e-4, atol=3e-4)
+    got32 = orc.triangle_attention(params, x, mask, starting=starting, dtype="float32")
+    np.testing.assert_allclose(got32, outs[starting], rtol=3e-4, atol=3e-4)
+
+
+def test_directions_differ_on_unstructured_input():
+    """A symmetric input hides a transposed contraction; the golden input is a
+    seeded normal draw, so the two directions must disagree."""
+    _, _, _, outs = load_trimul_golden("trimul_n12_c128.npz")
+    assert np.abs(outs["outgoing"] - outs["incoming"]).max() > 1e-3
+
+
+def test_ending_node_is_starting_node_on_transposed_input():
+    params, x, mask, _ = load_triatt_golden("triatt_n7_c8.npz")
+    end = orc.triangle_attention(params, x, mask, starting=False)
+    start_t = orc.triangle_attention(params, np.swapaxes(x, 1, 2), np.swapaxes(mask, 1, 2), starting=True)
+    np.testing.assert_allclose(end, np.swapaxes(start_t, 1, 2), rtol=1e-12, atol=1e-12)
+
+
+def test_incoming_is_outgoing_of_transposed_operands():
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((6, 6, 4))
+    b = rng.standard_normal((6, 6, 4))
+    inc = orc.triangle_contraction(a, b, "incoming")
+    out = orc.triangle_contraction(np.swapaxes(a, 0, 1), np.swapaxes(b, 0, 1), "outgoing")
+    np.testing.assert_allclose(inc, out, rtol=1e-12, atol=1e-12)
+
+
+def test_fully_masked_row_is_uniform_average():
+    """XLA-path convention: the -1e9 constant absorbs the scores in fp32, so a
+    row with no valid key becomes a uniform softmax over every key."""
+    rng = np.random.default_rng(3)
+    b, n, h, d = 1, 5, 2, 4
+    q = rng.standard_normal((b, n, h, n, d)).astype(np.float32)
+    k = rng.standard_normal((b, n, h, n, d)).astype(np.float32)
+    v = rng.standard_normal((b, n, h, n, d)).astype(np.float32)
+    tb = rng.standard_normal((b, 1, h, n, n)).astype(np.float32)
+    mask = np.ones((b, n, n), dtype=np.float32)
+    mask[0, 2, :] = 0.0
+    mb = (np.float32(1e9) * (mask - 1.0))[:, :, None, None, :]
+    out = orc.attention_core(q, k, v, tb, mb, dtype="float32")
+    np.testing.assert_allclose(out[0, 2], np.broadcast_to(v[0, 2].mean(axis=-2, keepdims=True), out[0, 2].shape),
+                               rtol=1e-5, atol=1e-5)
+
+
+def test_bf16_emulation_stays_close_to_truth():
+    rng = np.random.default_rng(0)
+    n = 24
+    params = orc.round_params(orc.random_trimul_params(rng, ln_noise=0.1), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    mask = orc.pad_mask(n, 3)
+    truth = orc.triangle_multiplication(params, x, mask, "outgoing", dtype="float64")
+    emu = orc.triangle_multiplication(params, x, mask, "outgoing", dtype="bfloat16")
+    err = orc.error_vs(truth, emu)
+    # the reference's own bf16 path sits about 5e-3 (mean) from the fp64 truth
+    assert err["max_abs_over_rms"] < 1e-1 and 1e-3 < err["mean_abs_over_rms"] < 1e-2, err
+
+
+def test_layer_norm_rounds_before_affine_in_bf16():
+    rng = np.random.default_rng(1)
+    x = orc.round_bf16(rng.standard_normal((4, 128)).astype(np.float32))
+    scale = orc.round_bf16(1.0 + 0.1 * rng.standard_normal(128).astype(np.float32))
+    bias = orc.round_bf16(0.1 * rng.standard_normal(128).astype(np.float32))
+    y = orc.layer_norm(x, scale, bias, 1e-5, dtype="bfloat16")
+    assert np.array_equal(y, orc.round_bf16(y))  # output is representable in bf16
+    y64 = orc.layer_norm(x, scale, bias, 1e-5, dtype="float64")
+    assert np.abs(y - y64).max() < 0.05
