@@ -74,6 +74,64 @@ class TrimulFinishArgs(C.Structure):
     ]
 
 
+class TriattArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("starting", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("inf", C.c_float), ("eps", C.c_float),
+        ("x", C.c_void_p), ("mask", C.c_void_p),
+        ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p), ("w_bias", C.c_void_p),
+        ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_g", C.c_void_p), ("w_o", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TriattProjectArgs(C.Structure):
+    _fields_ = [
+        ("n_outer", C.c_int32), ("n_inner", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("eps", C.c_float),
+        ("x", C.c_void_p), ("xs_outer", C.c_int64), ("xs_inner", C.c_int64),
+        ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p),
+        ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_bias", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("vt", C.c_void_p), ("bias", C.c_void_p),
+        ("ld", C.c_int64), ("bias_head_stride", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TriattCoreArgs(C.Structure):
+    _fields_ = [
+        ("n_i", C.c_int32), ("n_j", C.c_int32), ("n_k", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("vt", C.c_void_p), ("v_ld", C.c_int64),
+        ("bias", C.c_void_p), ("bias_ld", C.c_int64), ("bias_head_stride", C.c_int64),
+        ("mask", C.c_void_p), ("ms_i", C.c_int64), ("ms_k", C.c_int64), ("inf", C.c_float),
+        ("o", C.c_void_p), ("row_max", C.c_void_p), ("row_sum", C.c_void_p), ("unnormalized", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TriattFinishArgs(C.Structure):
+    _fields_ = [
+        ("n_outer", C.c_int32), ("n_inner", C.c_int32), ("eps", C.c_float),
+        ("o", C.c_void_p), ("x", C.c_void_p), ("xs_outer", C.c_int64), ("xs_inner", C.c_int64),
+        ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p), ("w_g", C.c_void_p), ("w_o", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p), ("os_outer", C.c_int64), ("os_inner", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+# C struct name -> ctypes mirror (tests compare sizeof on both sides)
+STRUCTS = {
+    "b200tri_trimul_args": TrimulArgs,
+    "b200tri_trimul_project_args": TrimulProjectArgs,
+    "b200tri_trimul_contract_args": TrimulContractArgs,
+    "b200tri_trimul_finish_args": TrimulFinishArgs,
+    "b200tri_triatt_args": TriattArgs,
+    "b200tri_triatt_project_args": TriattProjectArgs,
+    "b200tri_triatt_core_args": TriattCoreArgs,
+    "b200tri_triatt_finish_args": TriattFinishArgs,
+}
+
 # name -> (restype, argtypes); every symbol include/b200tri.h declares.
 SIGNATURES = {
     "b200tri_version": (C.c_int, []),
@@ -86,6 +144,14 @@ SIGNATURES = {
     "b200tri_trimul_contract": (C.c_int, [C.POINTER(TrimulContractArgs), C.c_void_p]),
     "b200tri_trimul_finish_workspace_bytes": (C.c_size_t, []),
     "b200tri_trimul_finish": (C.c_int, [C.POINTER(TrimulFinishArgs), C.c_void_p]),
+    "b200tri_triatt_workspace_bytes": (C.c_size_t, [C.c_int32]),
+    "b200tri_triatt_forward": (C.c_int, [C.POINTER(TriattArgs), C.c_void_p]),
+    "b200tri_triatt_project_workspace_bytes": (C.c_size_t, []),
+    "b200tri_triatt_project": (C.c_int, [C.POINTER(TriattProjectArgs), C.c_void_p]),
+    "b200tri_triatt_core_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "b200tri_triatt_core": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
+    "b200tri_triatt_finish_workspace_bytes": (C.c_size_t, []),
+    "b200tri_triatt_finish": (C.c_int, [C.POINTER(TriattFinishArgs), C.c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,483 @@
+// Triangle attention, core: for every row i, head h and query j
+//
+//   S[k]  = q[i,j,h,:] . k[i,k,h,:] + mask_bias[i,k] + tri_bias[h,j,k]
+//   o     = softmax_k(S) . v[i,k,h,:]
+//
+// Reference: _attention_block, src/foldjax/models/boltz2/models/triangle/
+// triangle_attention.py:428-455 (scores = q k^T + mask_bias + tri_bias in fp32,
+// softmax in fp32, P v, cast to the trunk dtype); the fused entry it replaces is
+// pallas_attention_core, triangle_attention_pallas.py:180.
+//
+// Flash-style: scores never leave the SM. One work item = (head h, group of NWG
+// consecutive rows i, tile of 128 queries j); each of the NWG softmax warpgroups
+// owns one row i, and all of them share the tri_bias tile [128 j x 64 k] of the
+// step, so the bias (the only operand that does not depend on i) crosses
+// L2 -> shared memory once per NWG rows.
+//
+//   warp 0        TMA producer: Q tiles per item; per 64-key step the bias tile and,
+//                 per row, K [64x32], V^T [32x64] and the mask-bias row
+//   warp 1        MMA issuer: S = Q K^T (bf16, 128x64x32) into TMEM, O += P V
+//                 (fp16, 128x32x64) with P read from TMEM
+//   warpgroups    softmax: one thread per query row. S from TMEM, + bias + mask,
+//                 running max with lazy rescale (the subtracted offset only moves
+//                 when the max grew by more than 2^8, so O stays in TMEM and is
+//                 rescaled rarely), exp2, row sum, P -> fp16 -> TMEM
+// TMEM per warpgroup: S 64 columns, P 32, O 32.
+//
+// Bound: not the tensor pipe. Per score the SM issues ~8 ALU/MUFU instructions
+// (unpack bias, add, max, fma, ex2, sum, half a cvt) against 128 tensor flops; at
+// 128 lanes/clk/SM that caps the tensor pipe near 25-30 % at head dim 32.
+#include <cuda_fp16.h>
+
+#include "host.cuh"
+#include "tc.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int NWG = 4;
+constexpr int KT = 64;
+constexpr int STAGES = 3;
+constexpr int THREADS = 64 + NWG * 128;
+constexpr int Q_BYTES = 128 * 64;    // [128 j][32 d] bf16
+constexpr int BIAS_BYTES = 128 * 128;  // [128 j][64 k] bf16
+constexpr int K_BYTES = KT * 64;     // [64 k][32 d] bf16
+constexpr int V_BYTES = 32 * 128;    // [32 d][64 k] fp16
+constexpr uint32_t TM_S = 0, TM_P = 64, TM_O = 96, TM_WG = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 5.5f;  // natural-log units, about 8 in log2
+
+struct Smem {
+  uint8_t q[NWG][Q_BYTES];
+  uint8_t bias[STAGES][BIAS_BYTES];
+  uint8_t k[STAGES][NWG][K_BYTES];
+  uint8_t v[STAGES][NWG][V_BYTES];
+  float mb[STAGES][NWG][KT];
+  uint64_t q_full, q_empty, st_full[STAGES], st_empty[STAGES], s_full[NWG], s_free[NWG], p_full[NWG], pv_done[NWG];
+  uint32_t tmem_base;
+};
+static_assert(sizeof(Smem) <= 232448, "shared memory budget");
+constexpr uint32_t STAGE_TX = BIAS_BYTES + NWG * (K_BYTES + V_BYTES + KT * 4);
+
+struct Params {
+  int n_i, n_j, n_k;  // rows, queries, keys
+  int heads;
+  int groups, tiles_j, steps;
+  long long total_items;
+  __nv_bfloat16* o;  // [n_i][n_j][128]
+  float* row_max;    // optional [n_i][heads][n_j]: offset m used (natural log units)
+  float* row_sum;    // optional: sum of exp(S - m)
+  int normalize;     // 1: o = O / l; 0: o = O (unnormalised, for merging across key tiles)
+  int* status;
+};
+
+__device__ __forceinline__ uint64_t desc_sw64(uint32_t saddr) { return umma_desc_kmajor(saddr, 64); }
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) { return umma_desc_kmajor(saddr, 128); }
+
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_m, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, ST_OK, 900);
+    return;
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_m);
+    mbar_init(&sm.q_full, 1);
+    mbar_init(&sm.q_empty, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.st_full[s], 1);
+      mbar_init(&sm.st_empty[s], 1 + NWG * 4);
+    }
+    for (int g = 0; g < NWG; ++g) {
+      mbar_init(&sm.s_full[g], 1);
+      mbar_init(&sm.s_free[g], 128);
+      mbar_init(&sm.p_full[g], 128);
+      mbar_init(&sm.pv_done[g], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+  const int items_per_head = p.groups * p.tiles_j;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0, item_it = 0;
+      bool alive = true;
+      for (long long item = blockIdx.x; item < p.total_items && alive; item += gridDim.x, ++item_it) {
+        const int h = static_cast<int>(item / items_per_head);
+        const int rem = static_cast<int>(item % items_per_head);
+        const int i0 = (rem / p.tiles_j) * NWG;
+        const int j0 = (rem % p.tiles_j) * 128;
+        if (!mbar_wait(&sm.q_empty, (item_it & 1) ^ 1, p.status, ST_TIMEOUT_PRODUCER)) break;
+        mbar_expect_tx(&sm.q_full, NWG * Q_BYTES);
+        for (int g = 0; g < NWG; ++g) tma_load_3d(sm.q[g], &tm_q, &sm.q_full, h * 32, j0, i0 + g);
+        for (int t = 0; t < p.steps; ++t) {
+          if (!mbar_wait(&sm.st_empty[stage], phase ^ 1, p.status, ST_TIMEOUT_PRODUCER)) {
+            alive = false;
+            break;
+          }
+          const int k0 = t * KT;
+          mbar_expect_tx(&sm.st_full[stage], STAGE_TX);
+          tma_load_3d(sm.bias[stage], &tm_b, &sm.st_full[stage], k0, j0, h);
+          for (int g = 0; g < NWG; ++g) {
+            tma_load_3d(sm.k[stage][g], &tm_k, &sm.st_full[stage], h * 32, k0, i0 + g);
+            tma_load_3d(sm.v[stage][g], &tm_v, &sm.st_full[stage], k0, h * 32, i0 + g);
+            tma_load_2d(sm.mb[stage][g], &tm_m, &sm.st_full[stage], k0, i0 + g);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, KT);
+      constexpr uint32_t idesc_pv = idesc_f16(128, 32);
+      int stage = 0;
+      uint32_t phase = 0, item_it = 0, g = 0;  // g: global step counter
+      bool alive = true;
+      auto issue_qk = [&](int wg, int st) {
+        const uint64_t adesc = desc_sw64(smem_u32(sm.q[wg]));
+        const uint64_t bdesc = desc_sw64(smem_u32(sm.k[st][wg]));
+        const uint32_t d = tmem_base + wg * TM_WG + TM_S;
+        umma_bf16_ss(d, adesc, bdesc, idesc_qk, 0);
+        umma_bf16_ss(d, umma_desc_advance(adesc, 32), umma_desc_advance(bdesc, 32), idesc_qk, 1);
+        umma_commit(&sm.s_full[wg]);
+      };
+      for (long long item = blockIdx.x; item < p.total_items && alive; item += gridDim.x, ++item_it) {
+        if (!mbar_wait(&sm.q_full, item_it & 1, p.status, ST_TIMEOUT_MMA)) break;
+        if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        for (int wg = 0; wg < NWG && alive; ++wg) {
+          if (!mbar_wait(&sm.s_free[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_MMA)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          issue_qk(wg, stage);
+        }
+        for (int t = 0; t < p.steps && alive; ++t, ++g) {
+          int nstage = stage + 1;
+          uint32_t nphase = phase;
+          if (nstage == STAGES) {
+            nstage = 0;
+            nphase ^= 1;
+          }
+          for (int wg = 0; wg < NWG; ++wg) {
+            if (!mbar_wait(&sm.p_full[wg], g & 1, p.status, ST_TIMEOUT_MMA)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t vdesc = desc_sw128(smem_u32(sm.v[stage][wg]));
+            const uint32_t d = tmem_base + wg * TM_WG + TM_O;
+            const uint32_t a = tmem_base + wg * TM_WG + TM_P;
+#pragma unroll
+            for (int k = 0; k < KT / 16; ++k)
+              umma_bf16_ts(d, a + k * 8, umma_desc_advance(vdesc, k * 32), idesc_pv, (t | k) != 0);
+            umma_commit(&sm.pv_done[wg]);
+            if (t + 1 < p.steps) {
+              if (wg == 0 && !mbar_wait(&sm.st_full[nstage], nphase, p.status, ST_TIMEOUT_MMA)) {
+                alive = false;
+                break;
+              }
+              if (!mbar_wait(&sm.s_free[wg], g & 1, p.status, ST_TIMEOUT_MMA)) {
+                alive = false;
+                break;
+              }
+              tc_fence_after();
+              issue_qk(wg, nstage);
+            }
+          }
+          if (!alive) break;
+          umma_commit(&sm.st_empty[stage]);
+          stage = nstage;
+          phase = nphase;
+        }
+        if (alive) umma_commit(&sm.q_empty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax
+    const int wg = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // query inside the tile = TMEM lane
+    const uint32_t t_wg = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + wg * TM_WG;
+    int stage = 0;
+    uint32_t phase = 0, g = 0;
+    bool alive = true;
+    for (long long item = blockIdx.x; item < p.total_items && alive; item += gridDim.x) {
+      const int h = static_cast<int>(item / items_per_head);
+      const int rem = static_cast<int>(item % items_per_head);
+      const int i = (rem / p.tiles_j) * NWG + wg;
+      const int j = (rem % p.tiles_j) * 128 + row;
+      float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
+      for (int t = 0; t < p.steps; ++t, ++g) {
+        if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_SOFTMAX) ||
+            !mbar_wait(&sm.s_full[wg], g & 1, p.status, ST_TIMEOUT_SOFTMAX)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        float u[KT];
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_wg + TM_S, r0);
+          tmem_ld32(t_wg + TM_S + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            u[e] = __uint_as_float(r0[e]);
+            u[32 + e] = __uint_as_float(r1[e]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&sm.s_free[wg]);
+        // + tri_bias (this thread's row of the shared tile) + mask bias (this row i)
+        const uint8_t* brow = sm.bias[stage];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 b4 = *reinterpret_cast<const uint4*>(brow + sw128_offset(row, c));
+          u[8 * c + 0] += bf16_lo(b4.x);
+          u[8 * c + 1] += bf16_hi(b4.x);
+          u[8 * c + 2] += bf16_lo(b4.y);
+          u[8 * c + 3] += bf16_hi(b4.y);
+          u[8 * c + 4] += bf16_lo(b4.z);
+          u[8 * c + 5] += bf16_hi(b4.z);
+          u[8 * c + 6] += bf16_lo(b4.w);
+          u[8 * c + 7] += bf16_hi(b4.w);
+        }
+        const float* mrow = sm.mb[stage][wg];
+        const bool masked = __any_sync(0xffffffffu, (mrow[lane] != 0.f) || (mrow[lane + 32] != 0.f));
+        if (masked) {
+#pragma unroll
+          for (int c = 0; c < KT / 4; ++c) {
+            const float4 m4 = *reinterpret_cast<const float4*>(mrow + 4 * c);
+            // (q.k + mask_bias) + tri_bias in the reference; a -1e9 absorbs either order in fp32
+            u[4 * c + 0] += m4.x;
+            u[4 * c + 1] += m4.y;
+            u[4 * c + 2] += m4.z;
+            u[4 * c + 3] += m4.w;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.st_empty[stage]);
+        float mx = u[0];
+#pragma unroll
+        for (int e = 1; e < KT; ++e) mx = fmaxf(mx, u[e]);
+        const float m_new = fmaxf(m_run, mx);
+        m_run = m_new;
+        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
+        float alpha = 1.f;
+        if (need) {
+          alpha = fast_exp2((m_used - m_new) * LOG2E);  // 0 on the first step (m_used = -inf)
+          m_used = m_new;
+          l *= alpha;
+        }
+        const float neg_m2 = -m_used * LOG2E;
+        uint32_t packed[KT / 2];
+#pragma unroll
+        for (int e = 0; e < KT / 2; ++e) {
+          const float p0 = fast_exp2(fmaf(u[2 * e], LOG2E, neg_m2));
+          const float p1 = fast_exp2(fmaf(u[2 * e + 1], LOG2E, neg_m2));
+          l += p0 + p1;
+          const __half2 h2 = __floats2half2_rn(p0, p1);
+          packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        // P buffer free and O stable once the previous step's P.V has completed.
+        if (!mbar_wait(&sm.pv_done[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_SOFTMAX)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        if (t > 0 && __any_sync(0xffffffffu, need)) {
+          uint32_t o[32];
+          tmem_ld32(t_wg + TM_O, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(t_wg + TM_O, o);
+        }
+        tmem_st32(t_wg + TM_P, packed);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[wg]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!alive) break;
+      // ---- item epilogue: O / l -> bf16 -> o[i][j][h*32 ..]
+      if (!mbar_wait(&sm.pv_done[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_SOFTMAX)) break;
+      tc_fence_after();
+      uint32_t o[32];
+      tmem_ld32(t_wg + TM_O, o);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (i < p.n_i && j < p.n_j) {
+        const float inv = p.normalize ? __fdividef(1.0f, l) : 1.0f;
+        uint4* dst = reinterpret_cast<uint4*>(p.o + (static_cast<long long>(i) * p.n_j + j) * 128 + h * 32);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16x2(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
+          dst[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (p.row_max) {
+          const long long si = (static_cast<long long>(i) * p.heads + h) * p.n_j + j;
+          p.row_max[si] = m_used;
+          p.row_sum[si] = l;
+        }
+      }
+    }
+  }
+
+  if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// mask_bias[i][k] = inf * (mask[i,k] - 1) for k < n_k, -infinity for the pitch
+// padding (keys that do not exist), built in fp32 like the reference
+// (triangle_attention.py:138-142).
+__global__ void mask_bias_kernel(const float* __restrict__ mask, long long ms_i, long long ms_k, int n_i, int n_k,
+                                 int ld, float inf, float* __restrict__ out) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(n_i) * ld) return;
+  const int i = static_cast<int>(idx / ld), k = static_cast<int>(idx % ld);
+  float v = -INFINITY;
+  if (k < n_k) v = mask ? inf * (mask[i * ms_i + k * ms_k] - 1.0f) : 0.0f;
+  out[idx] = v;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k) {
+  if (n_i <= 0 || n_k <= 0) return 0;
+  return static_cast<size_t>(n_i) * b200::round_up(n_k, 64) * sizeof(float) + 1024;
+}
+
+extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_stream_t stream_) {
+  using namespace b200;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "att core: null args");
+  B200_REQUIRE(a->q && a->k && a->vt && a->bias && a->o, B200TRI_ERR_INVALID, "att core: null pointer argument");
+  B200_REQUIRE(a->n_i > 0 && a->n_j > 0 && a->n_k > 0, B200TRI_ERR_INVALID, "att core: sizes must be positive");
+  B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
+               "att core: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
+  B200_REQUIRE(a->v_ld % 8 == 0 && a->bias_ld % 8 == 0 && a->bias_head_stride % 8 == 0 && a->v_ld >= a->n_k &&
+                   a->bias_ld >= a->n_k,
+               B200TRI_ERR_INVALID, "att core: pitches must be multiples of 8 elements and cover n_k");
+  B200_REQUIRE((a->row_max == nullptr) == (a->row_sum == nullptr), B200TRI_ERR_INVALID,
+               "att core: row_max and row_sum go together");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a->o) & 15) == 0, B200TRI_ERR_INVALID, "att core: o must be 16-byte aligned");
+  const size_t need = b200tri_triatt_core_workspace_bytes(a->n_i, a->n_k);
+  B200_REQUIRE(a->workspace && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
+               "att core: workspace of %zu bytes needed", need);
+  int* status = device_status_word();
+  B200_REQUIRE(status != nullptr, B200TRI_ERR_CUDA, "att core: no current CUDA device");
+
+  Carver ws(a->workspace);
+  const int ldm = round_up(a->n_k, 64);
+  float* mb = ws.take<float>(static_cast<size_t>(a->n_i) * ldm);
+  {
+    const long long total = static_cast<long long>(a->n_i) * ldm;
+    mask_bias_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        a->mask, a->ms_i, a->ms_k, a->n_i, a->n_k, ldm, a->inf, mb);
+    B200_CUDA_OK(cudaGetLastError());
+  }
+
+  CUtensorMap tm_q, tm_k, tm_v, tm_b, tm_m;
+  {
+    const uint64_t dims[3] = {128, (uint64_t)a->n_j, (uint64_t)a->n_i};
+    const uint64_t str[2] = {256, (uint64_t)a->n_j * 256};
+    const uint32_t box[3] = {32, 128, 1};
+    int rc = make_tmap(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B64);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[3] = {128, (uint64_t)a->n_k, (uint64_t)a->n_i};
+    const uint64_t str[2] = {256, (uint64_t)a->n_k * 256};
+    const uint32_t box[3] = {32, KT, 1};
+    int rc = make_tmap(&tm_k, a->k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B64);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)a->n_k, 128, (uint64_t)a->n_i};
+    const uint64_t str[2] = {(uint64_t)a->v_ld * 2, (uint64_t)a->v_ld * 2 * 128};
+    const uint32_t box[3] = {KT, 32, 1};
+    int rc = make_tmap(&tm_v, a->vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)a->n_k, (uint64_t)a->n_j, 4};
+    const uint64_t str[2] = {(uint64_t)a->bias_ld * 2, (uint64_t)a->bias_head_stride * 2};
+    const uint32_t box[3] = {KT, 128, 1};
+    int rc = make_tmap(&tm_b, a->bias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)ldm, (uint64_t)a->n_i};
+    const uint64_t str[1] = {(uint64_t)ldm * 4};
+    const uint32_t box[2] = {KT, 1};
+    int rc = make_tmap(&tm_m, mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dims, str, box, Swz::None);
+    if (rc) return rc;
+  }
+  Params p;
+  p.n_i = a->n_i;
+  p.n_j = a->n_j;
+  p.n_k = a->n_k;
+  p.heads = a->heads;
+  p.groups = (a->n_i + NWG - 1) / NWG;
+  p.tiles_j = (a->n_j + 127) / 128;
+  p.steps = (a->n_k + KT - 1) / KT;
+  p.total_items = static_cast<long long>(a->heads) * p.groups * p.tiles_j;
+  p.o = static_cast<__nv_bfloat16*>(a->o);
+  p.row_max = a->row_max;
+  p.row_sum = a->row_sum;
+  p.normalize = a->unnormalized ? 0 : 1;
+  p.status = status;
+
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    B200_CUDA_OK(cudaFuncSetAttribute(att_core_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+    configured[dev & 63] = true;
+  }
+  const long long grid = p.total_items < sm_count() ? p.total_items : sm_count();
+  att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm_k, tm_v, tm_b, tm_m, p);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200TRI_OK;
+}

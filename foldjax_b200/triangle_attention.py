@@ -1,0 +1,155 @@
+"""Triangle attention (starting / ending node) on B200 - host side.
+
+Mirrors ``triangle_attention_forward`` of the reference
+(src/foldjax/models/boltz2/models/triangle/triangle_attention.py:79-162) and the
+attention-core operator its fused backends implement
+(``pallas_attention_core``, triangle_attention_pallas.py:180; ``cueq_attention_core``,
+src/foldjax/models/_cueq.py:66). Same argument names and meaning; chunking knobs
+are accepted and ignored, as the reference's fused backends do.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Mapping
+
+import numpy as np
+import torch
+
+from . import _device as dev
+from . import _lib
+from .triangle import C_Z, _check_pair, _leaf, _ptr
+
+HEADS = 4
+HEAD_DIM = 32
+
+
+def triangle_attention_forward(
+    params: Mapping[str, Any],
+    x: Any,
+    mask: Any | None = None,
+    starting: bool = True,
+    inf: float = 1e9,
+    eps: float = 1e-5,
+    chunk_size: int = 128,
+    q_chunk_size: int | None = None,
+    matmul_precision: str = "highest",
+    triangle_backend: str = "b200",
+    *,
+    residual: Any | None = None,
+    out: torch.Tensor | None = None,
+):
+    """Boltz TriangleAttention, starting or ending node.
+
+    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``) bf16, ``mask`` ``[B, N, N]`` or
+    None (= ones). ``params`` is the reference's mapping ``{"layer_norm": {scale,
+    bias}, "linear": {kernel [128, 4]}, "mha": {"linear_q" | "linear_k" |
+    "linear_v" | "linear_g" | "linear_o": {kernel [128, 128]}}}``. Device tensors in
+    -> device tensor out; NumPy / CPU tensors in -> copied to the GPU and back.
+    """
+    if triangle_backend != "b200":
+        raise ValueError(f"Unsupported triangle_backend: {triangle_backend!r}")
+    if matmul_precision.lower() not in ("highest", "float32", "fp32", "default", "tensorfloat32", "tf32"):
+        raise ValueError(f"Unsupported matmul_precision: {matmul_precision!r}")
+    dev.require_cuda()
+    lib = _lib.load()
+    host_in = dev.is_host_array(x)
+    numpy_in = isinstance(x, np.ndarray)
+    xd, squeeze = _check_pair(dev.to_device(x, torch.bfloat16))
+    b, n = xd.shape[0], xd.shape[1]
+    md = None
+    if mask is not None:
+        md = dev.to_device(mask, torch.float32)
+        if md.dim() == 2:
+            md = md.unsqueeze(0)
+        if tuple(md.shape) != (b, n, n):
+            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
+    rd = None
+    if residual is not None:
+        rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+    if out is None:
+        out = torch.empty_like(xd)
+    else:
+        out, _ = _check_pair(out)
+    leaves = {
+        "norm_scale": _leaf(params, "layer_norm", "scale"),
+        "norm_bias": _leaf(params, "layer_norm", "bias"),
+        "w_bias": _leaf(params, "linear", "kernel"),
+        "w_q": _leaf(params, "mha", "linear_q", "kernel"),
+        "w_k": _leaf(params, "mha", "linear_k", "kernel"),
+        "w_v": _leaf(params, "mha", "linear_v", "kernel"),
+        "w_g": _leaf(params, "mha", "linear_g", "kernel"),
+        "w_o": _leaf(params, "mha", "linear_o", "kernel"),
+    }
+    if tuple(leaves["w_bias"].shape) != (C_Z, HEADS) or tuple(leaves["w_q"].shape) != (C_Z, HEADS * HEAD_DIM):
+        raise ValueError("libb200tri is built for 4 heads x 32 (linear [128,4], linear_q [128,128])")
+    nbytes = lib.b200tri_triatt_workspace_bytes(n)
+    ws = dev.workspace(nbytes, "triatt")
+    for bi in range(b):
+        args = _lib.TriattArgs(
+            n=n, starting=int(bool(starting)), heads=HEADS, head_dim=HEAD_DIM, inf=float(inf), eps=float(eps),
+            x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
+            residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+            **{k: v.data_ptr() for k, v in leaves.items()},
+        )
+        _lib.check(lib.b200tri_triatt_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))
+    result = out[0] if squeeze else out
+    if host_in:
+        host = result.float().cpu() if numpy_in else result.cpu()
+        return host.numpy() if numpy_in else host
+    return result
+
+
+def attention_core(q, k, v, tri_bias, mask_bias, scale: float | None = None):
+    """The attention-core operator: ``core(q, k, v, tri_bias, mask_bias[, scale]) -> out``.
+
+    q/k/v ``[B, I, H, J, D]`` device bf16 tensors (q pre-scaled unless ``scale`` is
+    given, the cuEquivariance convention), ``tri_bias [B, 1, H, J, J]``,
+    ``mask_bias [B, I, 1, 1, J]`` additive fp32 (0 / -inf constant). Returns
+    ``[B, I, H, J, D]`` in ``v.dtype``. Leading axes beyond five are folded into B.
+    This entry re-lays the operands out for the kernel (q,k -> [I,J,H*D], v ->
+    [I,H*D,J] fp16, bias -> [H,J,J]); the module-level forward avoids those copies
+    by producing that layout directly.
+    """
+    dev.require_cuda()
+    lib = _lib.load()
+    lead = q.shape[:-4]
+    qf = q.reshape((-1,) + tuple(q.shape[-4:]))
+    kf = k.reshape((-1,) + tuple(k.shape[-4:]))
+    vf = v.reshape((-1,) + tuple(v.shape[-4:]))
+    bf = tri_bias.reshape((-1,) + tuple(tri_bias.shape[-4:]))
+    mf = mask_bias.reshape((-1,) + tuple(mask_bias.shape[-4:]))
+    bsz, n_i, h, n_j, d = qf.shape
+    n_k = kf.shape[-2]
+    if (h, d) != (HEADS, HEAD_DIM):
+        raise ValueError(f"libb200tri is built for 4 heads x 32; got {h} x {d}")
+    if scale is not None:
+        qf = (qf.float() * float(scale)).to(torch.bfloat16)
+    ld = (n_k + 63) // 64 * 64
+    out = torch.empty((bsz, n_i, h, n_j, d), dtype=v.dtype, device=v.device)
+    nbytes = lib.b200tri_triatt_core_workspace_bytes(n_i, n_k)
+    ws = dev.workspace(nbytes, "triatt_core")
+    for bi in range(bsz):
+        q2 = qf[bi].permute(0, 2, 1, 3).reshape(n_i, n_j, h * d).to(torch.bfloat16).contiguous()
+        k2 = kf[bi].permute(0, 2, 1, 3).reshape(n_i, n_k, h * d).to(torch.bfloat16).contiguous()
+        v2 = torch.zeros(n_i, h * d, ld, dtype=torch.float16, device=v.device)
+        v2[:, :, :n_k] = vf[bi].permute(0, 1, 3, 2).reshape(n_i, h * d, n_k).to(torch.float16)
+        b2 = torch.zeros(h, n_j, ld, dtype=torch.bfloat16, device=v.device)
+        b2[:, :, :n_k] = bf[bi, 0].to(torch.bfloat16)
+        # additive mask -> the multiplicative form the kernel takes, with inf = max |mask_bias|
+        mb = mf[bi, :, 0, 0, :].float().contiguous()
+        big = float(mb.abs().max().item()) if mb.numel() else 0.0
+        m01 = (1.0 + mb / big).contiguous() if big > 0 else torch.ones_like(mb)
+        o2 = torch.empty(n_i, n_j, h * d, dtype=torch.bfloat16, device=v.device)
+        args = _lib.TriattCoreArgs(
+            n_i=n_i, n_j=n_j, n_k=n_k, heads=h, head_dim=d,
+            q=q2.data_ptr(), k=k2.data_ptr(), vt=v2.data_ptr(), v_ld=ld,
+            bias=b2.data_ptr(), bias_ld=ld, bias_head_stride=n_j * ld,
+            mask=m01.data_ptr(), ms_i=n_k, ms_k=1, inf=big if big > 0 else 1e9,
+            o=o2.data_ptr(), row_max=None, row_sum=None, unnormalized=0,
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+        )
+        _lib.check(lib.b200tri_triatt_core(C.byref(args), C.c_void_p(dev.stream_ptr())))
+        out[bi] = o2.reshape(n_i, n_j, h, d).permute(0, 2, 1, 3).to(v.dtype)
+    return out.reshape(tuple(lead) + tuple(out.shape[1:]))

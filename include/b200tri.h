@@ -156,6 +156,129 @@ typedef struct {
 size_t b200tri_trimul_finish_workspace_bytes(void);
 int b200tri_trimul_finish(const b200tri_trimul_finish_args* args, b200tri_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Triangle attention (starting / ending node).
+ * Replaces: triangle_attention_forward,
+ *   src/foldjax/models/boltz2/models/triangle/triangle_attention.py:79-162,
+ *   including _attention (:346-425) and the fused attention cores it can
+ *   dispatch to: pallas_attention_core (triangle_attention_pallas.py:180),
+ *   tokamax_attention_core (triangle_attention_tokamax.py:42) and
+ *   cueq_attention_core (src/foldjax/models/_cueq.py:66-121).
+ * Parameters in the reference's layout: layer_norm scale/bias [128]; `linear`
+ * (pair bias) [128, 4]; linear_q/k/v/g [128, 128] with heads-major columns;
+ * linear_o [128, 128]. starting = 0 computes the ending node: the same
+ * attention on the transposed pair tensor and mask, result transposed back.
+ * If `residual` is not NULL the kernel writes residual + update.
+ * --------------------------------------------------------------------- */
+typedef struct {
+  int32_t n;
+  int32_t starting; /* 1 = starting node, 0 = ending node */
+  int32_t heads;    /* 4 */
+  int32_t head_dim; /* 32 */
+  float inf;        /* mask constant (reference default 1e9) */
+  float eps;
+  const void* x; /* [n, n, 128] bf16 */
+  const float* mask;
+  const void* norm_scale;
+  const void* norm_bias;
+  const void* w_bias; /* params["linear"]["kernel"] */
+  const void* w_q;
+  const void* w_k;
+  const void* w_v;
+  const void* w_g;
+  const void* w_o;
+  const void* residual;
+  void* out;
+  void* workspace;
+  size_t workspace_bytes;
+} b200tri_triatt_args;
+
+size_t b200tri_triatt_workspace_bytes(int32_t n);
+int b200tri_triatt_forward(const b200tri_triatt_args* args, b200tri_stream_t stream);
+
+/* Stages, exposed for the context-parallel ring (the reference's
+ * ring_triangle_attention_2d, src/foldjax/models/_cp_attention.py:197-403, runs
+ * between the projections and the output stage).
+ *
+ * project: pair (o, t) is read at x + o*xs_outer + t*xs_inner. Writes
+ *   q, k   [n_outer][n_inner][128] bf16 (q already divided by sqrt(head_dim))
+ *   vt     [n_outer][128][ld] fp16 (V transposed per row o)
+ *   bias   [heads][n_outer][ld] bf16 at bias + h*bias_head_stride + o*ld + t
+ */
+typedef struct {
+  int32_t n_outer, n_inner, heads, head_dim;
+  float eps;
+  const void* x;
+  int64_t xs_outer, xs_inner;
+  const void* norm_scale;
+  const void* norm_bias;
+  const void* w_q;
+  const void* w_k;
+  const void* w_v;
+  const void* w_bias;
+  void* q;
+  void* k;
+  void* vt;
+  void* bias;
+  int64_t ld, bias_head_stride;
+  void* workspace;
+  size_t workspace_bytes;
+} b200tri_triatt_project_args;
+
+size_t b200tri_triatt_project_workspace_bytes(void);
+int b200tri_triatt_project(const b200tri_triatt_project_args* args, b200tri_stream_t stream);
+
+/* core: o[i][j][h*32+d] = sum_k softmax_k(q[i,j,h].k[i,k,h] + inf*(mask[i,k]-1) + bias[h,j,k]) v[i,k,h,d]
+ * for n_i rows, n_j queries, n_k keys (the operator the reference's attention
+ * cores implement, with q pre-scaled). mask is read at mask + i*ms_i + k*ms_k,
+ * NULL = ones. With row_max/row_sum not NULL the kernel also returns, per
+ * (i, h, j), the offset m it subtracted and l = sum_k exp(S - m); with
+ * `unnormalized` it leaves o = sum_k exp(S - m) v, so that partial results over
+ * key tiles can be merged (ring attention). */
+typedef struct {
+  int32_t n_i, n_j, n_k, heads, head_dim;
+  const void* q;  /* [n_i][n_j][128] */
+  const void* k;  /* [n_i][n_k][128] */
+  const void* vt; /* [n_i][128][v_ld] fp16 */
+  int64_t v_ld;
+  const void* bias; /* [heads][n_j][bias_ld] */
+  int64_t bias_ld, bias_head_stride;
+  const float* mask;
+  int64_t ms_i, ms_k;
+  float inf;
+  void* o;        /* [n_i][n_j][128] bf16 */
+  float* row_max; /* optional [n_i][heads][n_j] */
+  float* row_sum;
+  int32_t unnormalized;
+  void* workspace; /* b200tri_triatt_core_workspace_bytes(n_i, n_k) */
+  size_t workspace_bytes;
+} b200tri_triatt_core_args;
+
+size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k);
+int b200tri_triatt_core(const b200tri_triatt_core_args* args, b200tri_stream_t stream);
+
+/* finish: out = bf16(bf16(o * sigmoid(LN(x) @ w_g)) @ w_o) (+ residual); x and
+ * out/residual are addressed through (outer, inner) strides. */
+typedef struct {
+  int32_t n_outer, n_inner;
+  float eps;
+  const void* o; /* [n_outer][n_inner][128] */
+  const void* x;
+  int64_t xs_outer, xs_inner;
+  const void* norm_scale;
+  const void* norm_bias;
+  const void* w_g;
+  const void* w_o;
+  const void* residual;
+  void* out;
+  int64_t os_outer, os_inner;
+  void* workspace;
+  size_t workspace_bytes;
+} b200tri_triatt_finish_args;
+
+size_t b200tri_triatt_finish_workspace_bytes(void);
+int b200tri_triatt_finish(const b200tri_triatt_finish_args* args, b200tri_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,14 +52,9 @@ def test_struct_sizes_match_the_header():
         import pytest
 
         pytest.skip("gcc not available")
-    names = {
-        "b200tri_trimul_args": _lib.TrimulArgs,
-        "b200tri_trimul_project_args": _lib.TrimulProjectArgs,
-        "b200tri_trimul_contract_args": _lib.TrimulContractArgs,
-        "b200tri_trimul_finish_args": _lib.TrimulFinishArgs,
-    }
-    for extra in getattr(_lib, "EXTRA_STRUCTS", {}).items():
-        names[extra[0]] = extra[1]
+    names = dict(_lib.STRUCTS)
+    header = (ROOT / "include" / "b200tri.h").read_text()
+    assert set(re.findall(r"}\s*(b200tri_[a-z_]+_args);", header)) == set(names)
     src = '#include <stdio.h>\n#include "b200tri.h"\nint main(void){\n'
     for cname in names:
         src += f'  printf("{cname} %zu\\n", sizeof({cname}));\n'

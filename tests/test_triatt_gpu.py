@@ -1,0 +1,234 @@
+"""GPU parity of triangle attention against the oracle, through the C ABI.
+
+Tolerance: the benchmark's bf16 budget (mean-abs <= 2e-3 and max-abs <= 2e-2 of the
+output RMS, see conftest.assert_parity) against the oracle's bf16 emulation of the
+reference's XLA path. Rows of the attention that have no valid key hold
+"-1e9 absorbed in fp32" values in the reference; they are compared too (the kernel
+reproduces the uniform average) but with the same budget.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import assert_parity, load_triatt_golden
+from oracle import triangle_oracle as orc
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _run_forward(params, x, mask, starting, residual=None):
+    from foldjax_b200 import _lib
+    from foldjax_b200.triangle_attention import triangle_attention_forward
+
+    out = triangle_attention_forward(params, x, mask, starting=starting, residual=residual)
+    _lib.device_status()
+    return out
+
+
+def _valid_rows(mask, starting, shape):
+    has_key = mask.any(axis=2) if starting else mask.any(axis=1)
+    valid = has_key[:, :, None] if starting else has_key[:, None, :]
+    return np.broadcast_to(valid[..., None], shape)
+
+
+def test_projection_stage_matches_oracle(cuda_device):
+    from foldjax_b200 import _device as dev, _lib
+
+    lib = _lib.load()
+    rng = np.random.default_rng(21)
+    n = 136
+    params = orc.round_params(orc.random_triatt_params(rng, ln_noise=0.1, std=0.05), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    _, parts = orc.triangle_attention(params, x, None, True, dtype="bfloat16", return_parts=True)
+    P = dev.params_to_device(params)
+    xd = dev.to_device(x, torch.bfloat16)[0]
+    ld = (n + 63) // 64 * 64
+    q = torch.empty(n, n, 128, dtype=torch.bfloat16, device=cuda_device)
+    k = torch.empty_like(q)
+    vt = torch.zeros(n, 128, ld, dtype=torch.float16, device=cuda_device)
+    bias = torch.zeros(4, n, ld, dtype=torch.bfloat16, device=cuda_device)
+    nb = lib.b200tri_triatt_project_workspace_bytes()
+    ws = torch.empty(nb + 1024, dtype=torch.uint8, device=cuda_device)
+    args = _lib.TriattProjectArgs(
+        n_outer=n, n_inner=n, heads=4, head_dim=32, eps=1e-5,
+        x=xd.data_ptr(), xs_outer=n * 128, xs_inner=128,
+        norm_scale=P["layer_norm"]["scale"].data_ptr(), norm_bias=P["layer_norm"]["bias"].data_ptr(),
+        w_q=P["mha"]["linear_q"]["kernel"].data_ptr(), w_k=P["mha"]["linear_k"]["kernel"].data_ptr(),
+        w_v=P["mha"]["linear_v"]["kernel"].data_ptr(), w_bias=P["linear"]["kernel"].data_ptr(),
+        q=q.data_ptr(), k=k.data_ptr(), vt=vt.data_ptr(), bias=bias.data_ptr(), ld=ld, bias_head_stride=n * ld,
+        workspace=dev.aligned_ptr(ws), workspace_bytes=nb,
+    )
+    _lib.check(lib.b200tri_triatt_project(C.byref(args), C.c_void_p(dev.stream_ptr())))
+    _lib.device_status()
+    # oracle parts are [B, I, H, J, D]
+    q_ref = parts["q"][0].transpose(0, 2, 1, 3).reshape(n, n, 128)
+    k_ref = parts["k"][0].transpose(0, 2, 1, 3).reshape(n, n, 128)
+    v_ref = parts["v"][0].transpose(0, 1, 3, 2).reshape(n, 128, n)
+    b_ref = parts["tri_bias"][0, 0]
+    print(assert_parity(q_ref, q.float().cpu().numpy(), label="q", mean_tol=2e-4))
+    print(assert_parity(k_ref, k.float().cpu().numpy(), label="k", mean_tol=2e-4))
+    print(assert_parity(v_ref, vt[:, :, :n].float().cpu().numpy(), label="vT", mean_tol=2e-4))
+    print(assert_parity(b_ref, bias[:, :, :n].float().cpu().numpy(), label="bias", mean_tol=2e-4))
+
+
+@pytest.mark.parametrize("n_i,n_j,n_k", [(4, 128, 64), (9, 200, 200), (16, 256, 320)])
+def test_core_matches_dense_attention(cuda_device, n_i, n_j, n_k):
+    """The attention-core operator on its own, with large biases so the running
+    max moves (exercises the rescale), random key masks and one row with no
+    valid key (uniform average in the XLA-path convention)."""
+    from foldjax_b200 import _device as dev, _lib
+
+    lib = _lib.load()
+    rng = np.random.default_rng(n_i * 1000 + n_k)
+    h, d = 4, 32
+    q = orc.round_bf16(rng.normal(size=(n_i, n_j, h * d), scale=0.6).astype(np.float32))
+    k = orc.round_bf16(rng.normal(size=(n_i, n_k, h * d), scale=0.6).astype(np.float32))
+    v = orc.round_bf16(rng.normal(size=(n_i, n_k, h * d), scale=1.0).astype(np.float32))
+    bias = orc.round_bf16(rng.normal(size=(h, n_j, n_k), scale=4.0).astype(np.float32))
+    # keys sorted by a trend so later tiles raise the maximum
+    bias += orc.round_bf16(np.linspace(-6, 6, n_k, dtype=np.float32))[None, None, :]
+    bias = orc.round_bf16(bias)
+    keep = rng.random((n_i, n_k)) > 0.2
+    keep[:, 0] = True
+    keep[n_i - 1, :] = False  # a row with no valid key
+    mask = keep.astype(np.float32)
+    # dense fp32 reference in the reference's operand order
+    q5 = q.reshape(n_i, n_j, h, d).transpose(0, 2, 1, 3)[None]
+    k5 = k.reshape(n_i, n_k, h, d).transpose(0, 2, 1, 3)[None]
+    v5 = v.reshape(n_i, n_k, h, d).transpose(0, 2, 1, 3)[None]
+    mb = (np.float32(1e9) * (mask - 1.0))[None, :, None, None, :]
+    ref = orc.attention_core(q5, k5, v5, bias[None, None], mb, dtype="bfloat16")[0]  # [I,H,J,D]
+    ref = ref.transpose(0, 2, 1, 3).reshape(n_i, n_j, h * d)
+
+    ld = (n_k + 63) // 64 * 64
+    qd = dev.to_device(q, torch.bfloat16)
+    kd = dev.to_device(k, torch.bfloat16)
+    vt = torch.zeros(n_i, h * d, ld, dtype=torch.float16, device=cuda_device)
+    vt[:, :, :n_k] = torch.from_numpy(np.ascontiguousarray(v.transpose(0, 2, 1))).to(cuda_device).half()
+    bd = torch.zeros(h, n_j, ld, dtype=torch.bfloat16, device=cuda_device)
+    bd[:, :, :n_k] = torch.from_numpy(bias).to(cuda_device).bfloat16()
+    md = dev.to_device(mask, torch.float32)
+    o = torch.full((n_i, n_j, h * d), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    rmax = torch.zeros(n_i, h, n_j, dtype=torch.float32, device=cuda_device)
+    rsum = torch.zeros_like(rmax)
+    nb = lib.b200tri_triatt_core_workspace_bytes(n_i, n_k)
+    ws = torch.empty(nb + 1024, dtype=torch.uint8, device=cuda_device)
+    args = _lib.TriattCoreArgs(
+        n_i=n_i, n_j=n_j, n_k=n_k, heads=h, head_dim=d,
+        q=qd.data_ptr(), k=kd.data_ptr(), vt=vt.data_ptr(), v_ld=ld,
+        bias=bd.data_ptr(), bias_ld=ld, bias_head_stride=n_j * ld,
+        mask=md.data_ptr(), ms_i=n_k, ms_k=1, inf=1e9,
+        o=o.data_ptr(), row_max=rmax.data_ptr(), row_sum=rsum.data_ptr(), unnormalized=0,
+        workspace=dev.aligned_ptr(ws), workspace_bytes=nb,
+    )
+    _lib.check(lib.b200tri_triatt_core(C.byref(args), C.c_void_p(dev.stream_ptr())))
+    _lib.device_status()
+    got = o.float().cpu().numpy()
+    print(assert_parity(ref, got, label=f"core {n_i}x{n_j}x{n_k}"))
+    # softmax statistics: log-sum-exp of the scores per (i, h, j)
+    s = np.einsum("ihjd,ihkd->ihjk", q5[0].astype(np.float64), k5[0].astype(np.float64))
+    s = s + mb[0].astype(np.float64) + bias[None].astype(np.float64)
+    lse_ref = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    lse_got = rmax.cpu().numpy().astype(np.float64) + np.log(rsum.cpu().numpy().astype(np.float64))
+    valid = keep.any(axis=1)
+    np.testing.assert_allclose(lse_got[valid], lse_ref[valid], rtol=0, atol=5e-3)
+
+
+@pytest.mark.parametrize("starting", [True, False])
+def test_golden_case_through_the_plugin(cuda_device, starting):
+    params, x, mask, outs = load_triatt_golden("triatt_n12_c128.npz")
+    params = orc.round_params(params, "bfloat16")
+    xb = orc.round_bf16(x)
+    emu = orc.triangle_attention(params, xb, mask, starting=starting, dtype="bfloat16")
+    got = _run_forward(params, xb, mask, starting)
+    valid = _valid_rows(mask, starting, emu.shape)
+    print(assert_parity(emu, got, where=valid, label=f"golden starting={starting}"))
+    err = orc.error_vs(outs[starting][valid], got[valid])
+    assert err["mean_abs_over_rms"] < 3e-2, err
+
+
+@pytest.mark.parametrize("n,n_pad", [(64, 0), (128, 8), (200, 13), (256, 64)])
+@pytest.mark.parametrize("starting", [True, False])
+def test_forward_matches_oracle(cuda_device, n, n_pad, starting):
+    rng = np.random.default_rng(200 + n)
+    params = orc.round_params(orc.random_triatt_params(rng, ln_noise=0.1, std=0.05), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    mask = orc.pad_mask(n, n_pad)
+    emu = orc.triangle_attention(params, x, mask, starting=starting, dtype="bfloat16")
+    got = _run_forward(params, x, mask, starting)
+    valid = _valid_rows(mask, starting, emu.shape)
+    print(assert_parity(emu, got, where=valid, label=f"triatt n={n} starting={starting}"))
+    if n_pad:  # rows with no valid key: uniform average over all keys, like the XLA path
+        print(assert_parity(emu, got, where=~valid, label="  fully masked rows", mean_tol=5e-3))
+    truth = orc.triangle_attention(params, x, mask, starting=starting, dtype="float64")
+    e_truth = orc.error_vs(truth[valid], got[valid])
+    e_emu = orc.error_vs(truth[valid], emu[valid])
+    assert e_truth["mean_abs_over_rms"] <= 1.25 * e_emu["mean_abs_over_rms"] + 1e-4, (e_truth, e_emu)
+
+
+def test_config2_shape_and_ending_is_transposed_starting(cuda_device):
+    """Benchmark config 2 (N=512, last 64 tokens padded, seed 1): ending node ==
+    starting node on the transposed input, and sampled rows agree with the oracle."""
+    from foldjax_b200 import _device as dev, _lib
+    from foldjax_b200.triangle_attention import triangle_attention_forward
+
+    rng = np.random.default_rng(1)
+    n = 512
+    params_np = orc.round_params(orc.random_triatt_params(rng), "bfloat16")
+    params = dev.params_to_device(params_np)
+    x_np = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    mask_np = orc.pad_mask(n, 64)
+    x = dev.to_device(x_np, torch.bfloat16)
+    mask = dev.to_device(mask_np, torch.float32)
+    end = triangle_attention_forward(params, x, mask, starting=False)
+    start_t = triangle_attention_forward(params, x.transpose(1, 2).contiguous(), mask.transpose(1, 2).contiguous(),
+                                         starting=True)
+    _lib.device_status()
+    assert torch.equal(end, start_t.transpose(1, 2))
+    # starting node, sampled rows i against the oracle (rows are independent)
+    start = triangle_attention_forward(params, x, mask, starting=True)
+    rows = [0, 255, 447]
+    emu, parts = orc.triangle_attention(params_np, x_np, mask_np, True, dtype="bfloat16", return_parts=True)
+    got = start[0, rows].float().cpu().numpy()
+    print(assert_parity(emu[0, rows], got, label="config 2 sampled rows"))
+
+
+def test_attention_core_operator_signature(cuda_device):
+    """core(q, k, v, tri_bias, mask_bias) with the reference's 5-D operands."""
+    from foldjax_b200.triangle_attention import attention_core
+    from foldjax_b200 import _lib
+
+    rng = np.random.default_rng(9)
+    b, n, h, d = 1, 96, 4, 32
+    q = orc.round_bf16(rng.normal(size=(b, n, h, n, d), scale=0.5).astype(np.float32))
+    k = orc.round_bf16(rng.normal(size=(b, n, h, n, d), scale=0.5).astype(np.float32))
+    v = orc.round_bf16(rng.normal(size=(b, n, h, n, d)).astype(np.float32))
+    tb = orc.round_bf16(rng.normal(size=(b, 1, h, n, n), scale=2.0).astype(np.float32))
+    keep = rng.random((b, n, n)) > 0.15
+    keep[..., 0] = True
+    mb = np.where(keep[:, :, None, None, :], np.float32(0), np.float32(-1e9))
+    ref = orc.attention_core(q, k, v, tb, mb, dtype="bfloat16")
+    t = lambda a, dt: torch.from_numpy(a).to(cuda_device).to(dt)
+    got = attention_core(t(q, torch.bfloat16), t(k, torch.bfloat16), t(v, torch.bfloat16), t(tb, torch.bfloat16),
+                         t(mb, torch.float32))
+    _lib.device_status()
+    assert got.shape == ref.shape and got.dtype == torch.bfloat16
+    print(assert_parity(ref, got.float().cpu().numpy(), label="attention_core operator"))
+
+
+def test_mask_none_residual_and_determinism(cuda_device):
+    rng = np.random.default_rng(6)
+    n = 80
+    params = orc.round_params(orc.random_triatt_params(rng), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    a = _run_forward(params, x, None, True)
+    b = _run_forward(params, x, np.ones((1, n, n), np.float32), True)
+    assert np.array_equal(a, b)
+    c = _run_forward(params, x, None, True, residual=x)
+    np.testing.assert_array_equal(c, orc.round_bf16(x + a))
+    assert np.array_equal(a, _run_forward(params, x, None, True))
