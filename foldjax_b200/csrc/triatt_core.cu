@@ -25,7 +25,7 @@
 // TMEM per warpgroup: S 64 columns, P 32, O 32.
 //
 // Bound: not the tensor pipe. Per score the SM issues ~8 ALU/MUFU instructions
-// (unpack bias, add, max, fma, ex2, sum, half a cvt) against 128 tensor flops; at
+// (unpack bias, add, max, sub, mul, ex2, sum, half a cvt) against 128 tensor flops; at
 // 128 lanes/clk/SM that caps the tensor pipe near 25-30 % at head dim 32.
 #include <cuda_fp16.h>
 
@@ -299,12 +299,14 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           m_used = m_new;
           l *= alpha;
         }
-        const float neg_m2 = -m_used * LOG2E;
+        // exp(u - m) as exp2((u - m) * log2e): the subtraction first, so that a row
+        // whose maximum is the -1e9 mask constant (no valid key) still gets exact
+        // zeros in the exponent; folding m * log2e into an fma loses 2^-24 * 1e9.
         uint32_t packed[KT / 2];
 #pragma unroll
         for (int e = 0; e < KT / 2; ++e) {
-          const float p0 = fast_exp2(fmaf(u[2 * e], LOG2E, neg_m2));
-          const float p1 = fast_exp2(fmaf(u[2 * e + 1], LOG2E, neg_m2));
+          const float p0 = fast_exp2((u[2 * e] - m_used) * LOG2E);
+          const float p1 = fast_exp2((u[2 * e + 1] - m_used) * LOG2E);
           l += p0 + p1;
           const __half2 h2 = __floats2half2_rn(p0, p1);
           packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
