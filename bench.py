@@ -1,0 +1,299 @@
+"""Benchmark of the Pairformer triangle hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens 3072] [--impl reference]
+
+One "step" = the triangle path of one Pairformer block (tri-mult outgoing,
+tri-mult incoming, tri-attention starting node, tri-attention ending node, each
+with its residual add) on a synthetic pair tensor z[N,N,128] in bf16 with
+random-init N(0, 0.02) weights and a pad mask on the last ~2 % of tokens - the
+per-block work of the 48-block trunk at N = 3012 -> 3072 tokens.
+
+Prints ONE JSON line (rank 0): metric = achieved TFLOP/s over the algorithmic
+flops of the four ops, ms_per_step = block milliseconds. With N > 1 GPUs every
+rank runs its own complex (replicas, weak scaling); the value is the aggregate.
+`--impl reference` times the CPU restatement of the reference's XLA path (the
+reference's JAX code cannot run here: JAX is not installed) on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "pairformer_triangle_block_tflops"
+UNIT = "TFLOP/s"
+
+
+def block_flops(n: int) -> float:
+    return 2.0 * (256.0 * n**3 + 196608.0 * n**2) + 2.0 * (512.0 * n**3 + 164864.0 * n**2)
+
+
+def make_params(rng: np.random.Generator) -> dict:
+    from foldjax_b200.synthetic import block_params
+
+    return block_params(rng)
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ----------------------------------------------------------------------- CPU arm
+def cpu_block(params, z, mask, dtype="float32"):
+    """The oracle's restatement of the reference's XLA path, four ops with residuals."""
+    from oracle import triangle_oracle as orc
+
+    z = z + orc.triangle_multiplication(params["tri_mul_out"], z, mask, "outgoing", dtype=dtype)
+    z = z + orc.triangle_multiplication(params["tri_mul_in"], z, mask, "incoming", dtype=dtype)
+    z = z + orc.triangle_attention(params["tri_att_start"], z, mask, starting=True, dtype=dtype)
+    z = z + orc.triangle_attention(params["tri_att_end"], z, mask, starting=False, dtype=dtype)
+    return z
+
+
+def time_cpu(n: int, reps: int, warmup: int = 0) -> tuple[float, float]:
+    """(seconds per block, TFLOP/s) of the CPU restatement at n tokens, fp32, BLAS-threaded."""
+    from foldjax_b200.synthetic import pad_mask
+
+    rng = np.random.default_rng(2)
+    params = make_params(rng)
+    z = rng.standard_normal((1, n, n, 128)).astype(np.float32)
+    mask = pad_mask(n, max(1, n // 50))
+    for _ in range(warmup):
+        cpu_block(params, z, mask)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_block(params, z, mask)
+    dt = (time.perf_counter() - t0) / reps
+    return dt, block_flops(n) / dt / 1e12
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    n = args.cpu_tokens
+    secs, tf = time_cpu(n, reps=max(1, args.steps), warmup=min(1, args.warmup))
+    sample = f"one block's four triangle ops at N={n} fp32 (bounded sample of the N={args.tokens} workload)"
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"pairformer-triangle-block N={args.tokens} c_z=128 4x32 heads (cfg 4 per block)",
+                   "cpu_sample_tokens": n},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference jnp path unavailable on this box (JAX not installed); NumPy restatement timed instead",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """nvidia-smi samples of one GPU during the timed region."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_gpu(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from foldjax_b200 import _device as dev
+    from foldjax_b200 import _lib
+    from foldjax_b200.block import triangle_block_forward
+    from foldjax_b200.synthetic import pad_mask
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _lib.load()
+
+    n = args.tokens
+    rng = np.random.default_rng(3 + rank)
+    params = dev.params_to_device(make_params(rng))
+    n_pad = n - int(round(n * 3012 / 3072)) if n >= 64 else 0
+    mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
+    gen = torch.Generator(device="cuda").manual_seed(3 + rank)
+    z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
+    mask = mask_host.cuda()
+    z_host = torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True)
+    z_host.copy_(z)
+    out_host = torch.empty_like(z_host).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing (inputs already in HBM)
+    for _ in range(args.warmup):
+        triangle_block_forward(params, z, mask)
+    lib.b200tri_timing_reset()
+    lib.b200tri_timing_enable(1)
+    launches0 = lib.b200tri_launch_count()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        result = triangle_block_forward(params, z, mask)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    launches = int(lib.b200tri_launch_count() - launches0)
+    lib.b200tri_timing_enable(0)
+    ktimes = _lib.kernel_times()
+    _lib.device_status()
+    assert torch.isfinite(result.float()).all(), "non-finite values in the block output"
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    e2e_steps = max(1, min(args.steps, 3))
+    for _ in range(min(args.warmup, 1)):
+        triangle_block_forward(params, z_host, mask_host, out=out_host)
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_steps):
+        triangle_block_forward(params, z_host, mask_host, out=out_host)
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / args.steps
+    flops = block_flops(n)
+    peaks, peak_kind = measured_peaks()
+    core_ms, core_n = ktimes["triatt_core"]
+    core_avg = core_ms / max(core_n, 1)
+    core_flops = 4.0 * n**3 * 128.0  # QK^T + PV per launch
+    achieved = core_flops / (core_avg * 1e-3) / 1e12 if core_avg else None
+    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
+    shares = {k: round(v[0] / max(sum(t[0] for t in ktimes.values()), 1e-9), 4) for k, v in ktimes.items()}
+    cores = len(os.sched_getaffinity(0))
+    cpu_secs, cpu_tf = time_cpu(args.cpu_tokens, reps=1) if world == 1 and not args.no_cpu else (None, None)
+    line = {
+        "metric": METRIC, "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
+                        "tri-mult out+in, tri-attn start+end, residual adds fused",
+            "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops,
+            "parallelism": "single GPU" if world == 1 else f"{world} replicas, one complex per GPU, no collective",
+            "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
+        },
+        "clocks": clocks,
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(z_host.numel() * 2 + mask_host.numel() * 4),
+                "d2h_bytes_per_step": int(out_host.numel() * 2)},
+        "gpu_launches": launches,
+        "roofline": {
+            "kernel": "att_core_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": (achieved / peak) if achieved else None, "peak_kind": f"{peak_kind} sustained bf16",
+            "traffic": None, "avg_launch_ms": core_avg, "launches": core_n,
+            "note": "binding resource is the MUFU/ALU softmax path (4*N^3 exps), not the tensor pipe",
+        },
+        "kernel_ms_per_launch": {k: round(v[0] / max(v[1], 1), 4) for k, v in ktimes.items()},
+        "kernel_time_share": shares,
+        "cpu_baseline": None if cpu_tf is None else {
+            "value": cpu_tf, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"one block's four triangle ops at N={args.cpu_tokens} fp32 via the NumPy restatement "
+                      f"({cpu_secs:.1f} s)"},
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=3072)
+    ap.add_argument("--cpu-tokens", type=int, default=320, help="size of the bounded CPU sample")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

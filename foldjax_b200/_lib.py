@@ -137,6 +137,10 @@ SIGNATURES = {
     "b200tri_version": (C.c_int, []),
     "b200tri_last_error": (C.c_char_p, []),
     "b200tri_device_status": (C.c_int, []),
+    "b200tri_launch_count": (C.c_uint64, []),
+    "b200tri_timing_enable": (C.c_int, [C.c_int32]),
+    "b200tri_timing_reset": (C.c_int, []),
+    "b200tri_timing_read": (C.c_int, [C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_int32)]),
     "b200tri_trimul_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_trimul_forward": (C.c_int, [C.POINTER(TrimulArgs), C.c_void_p]),
     "b200tri_trimul_project_workspace_bytes": (C.c_size_t, []),
@@ -189,3 +193,17 @@ def device_status() -> int:
         msg = load().b200tri_last_error()
         raise B200TriError(ERR_TIMEOUT, msg.decode() if msg else f"device status {st}")
     return st
+
+
+KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish")
+
+
+def kernel_times() -> dict[str, tuple[float, int]]:
+    """{kernel: (total ms, launches)} since the last timing reset (synchronises)."""
+    lib = load()
+    out = {}
+    for name in KERNELS:
+        ms, n = C.c_double(0.0), C.c_int32(0)
+        check(lib.b200tri_timing_read(name.encode(), C.byref(ms), C.byref(n)))
+        out[name] = (ms.value, n.value)
+    return out

@@ -65,4 +65,16 @@ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 int sm_count();
 
+// Launch accounting and optional per-kernel event timing.
+enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
+                K_TRIATT_FINISH, K_COUNT };
+void count_launch(int n = 1);
+struct TimedLaunch {  // brackets the launches made during its lifetime
+  int id;
+  cudaStream_t stream;
+  cudaEvent_t start = nullptr;
+  TimedLaunch(int id, cudaStream_t stream);
+  ~TimedLaunch();
+};
+
 }  // namespace b200

@@ -1,6 +1,8 @@
 // Parameter repacking kernels (see pack.cuh).
 #include "pack.cuh"
 
+#include "host.cuh"
+
 namespace b200 {
 
 namespace {
@@ -25,12 +27,15 @@ __global__ void pack_copy_words_kernel(const uint32_t* __restrict__ src, uint32_
 void pack_transpose(const __nv_bfloat16* src, int src_ld, int col0, int ncols, __nv_bfloat16* dst,
                     cudaStream_t stream, float scale) {
   const int total = ncols * 128;
+  count_launch();
   pack_transpose_kernel<<<(total + 255) / 256, 256, 0, stream>>>(src, src_ld, col0, ncols, dst, scale);
 }
 void pack_zero(__nv_bfloat16* dst, int count, cudaStream_t stream) {
+  count_launch();
   pack_zero_kernel<<<(count + 255) / 256, 256, 0, stream>>>(dst, count);
 }
 void pack_copy_words(const void* src, void* dst, int nwords, cudaStream_t stream) {
+  count_launch();
   pack_copy_words_kernel<<<(nwords + 255) / 256, 256, 0, stream>>>(static_cast<const uint32_t*>(src),
                                                                    static_cast<uint32_t*>(dst), nwords);
 }

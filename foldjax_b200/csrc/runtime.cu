@@ -2,7 +2,12 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <string.h>
+
+#include <atomic>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "host.cuh"
 
@@ -49,6 +54,35 @@ int sm_count() {
   return cache[dev];
 }
 
+static std::atomic<uint64_t> g_launches{0};
+static std::atomic<int> g_timing{0};
+static std::mutex g_timing_mu;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events[K_COUNT];
+static const char* const kKernelNames[K_COUNT] = {"trimul_project", "trimul_contract", "trimul_finish",
+                                                  "triatt_project", "triatt_core",     "triatt_finish"};
+
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+TimedLaunch::TimedLaunch(int id_, cudaStream_t stream_) : id(id_), stream(stream_) {
+  if (!g_timing.load(std::memory_order_relaxed)) return;
+  if (cudaEventCreate(&start) != cudaSuccess) {
+    start = nullptr;
+    return;
+  }
+  cudaEventRecord(start, stream);
+}
+TimedLaunch::~TimedLaunch() {
+  if (!start) return;
+  cudaEvent_t stop = nullptr;
+  if (cudaEventCreate(&stop) != cudaSuccess) {
+    cudaEventDestroy(start);
+    return;
+  }
+  cudaEventRecord(stop, stream);
+  std::lock_guard<std::mutex> lock(g_timing_mu);
+  g_events[id].emplace_back(start, stop);
+}
+
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   static std::mutex mu;
@@ -91,6 +125,45 @@ extern "C" {
 int b200tri_version(void) { return 100; }
 
 const char* b200tri_last_error(void) { return b200::get_error(); }
+
+uint64_t b200tri_launch_count(void) { return b200::g_launches.load(); }
+
+int b200tri_timing_enable(int32_t on) {
+  b200::g_timing.store(on ? 1 : 0);
+  return B200TRI_OK;
+}
+
+int b200tri_timing_reset(void) {
+  std::lock_guard<std::mutex> lock(b200::g_timing_mu);
+  for (auto& v : b200::g_events) {
+    for (auto& e : v) {
+      cudaEventDestroy(e.first);
+      cudaEventDestroy(e.second);
+    }
+    v.clear();
+  }
+  return B200TRI_OK;
+}
+
+int b200tri_timing_read(const char* kernel, double* total_ms, int32_t* launches) {
+  using namespace b200;
+  B200_REQUIRE(kernel && total_ms && launches, B200TRI_ERR_INVALID, "timing_read: null argument");
+  int id = -1;
+  for (int i = 0; i < K_COUNT; ++i)
+    if (strcmp(kernel, kKernelNames[i]) == 0) id = i;
+  B200_REQUIRE(id >= 0, B200TRI_ERR_INVALID, "timing_read: unknown kernel name '%s'", kernel);
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lock(g_timing_mu);
+  double sum = 0.0;
+  for (auto& e : g_events[id]) {
+    float ms = 0.f;
+    B200_CUDA_OK(cudaEventElapsedTime(&ms, e.first, e.second));
+    sum += ms;
+  }
+  *total_ms = sum;
+  *launches = static_cast<int32_t>(g_events[id].size());
+  return B200TRI_OK;
+}
 
 int b200tri_device_status(void) {
   int* w = b200::device_status_word();

@@ -415,6 +415,7 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   float* mb = ws.take<float>(static_cast<size_t>(a->n_i) * ldm);
   {
     const long long total = static_cast<long long>(a->n_i) * ldm;
+    count_launch();
     mask_bias_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
         a->mask, a->ms_i, a->ms_k, a->n_i, a->n_k, ldm, a->inf, mb);
     B200_CUDA_OK(cudaGetLastError());
@@ -479,7 +480,11 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
     configured[dev & 63] = true;
   }
   const long long grid = p.total_items < sm_count() ? p.total_items : sm_count();
-  att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm_k, tm_v, tm_b, tm_m, p);
+  {
+    TimedLaunch timed(K_TRIATT_CORE, stream);
+    count_launch();
+    att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm_k, tm_v, tm_b, tm_m, p);
+  }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
 }

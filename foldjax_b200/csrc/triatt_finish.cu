@@ -341,7 +341,11 @@ extern "C" int b200tri_triatt_finish(const b200tri_triatt_finish_args* a, b200tr
     configured[dev & 63] = true;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-  att_finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_o, tm_w, p);
+  {
+    TimedLaunch timed(K_TRIATT_FINISH, stream);
+    count_launch();
+    att_finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_o, tm_w, p);
+  }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
 }

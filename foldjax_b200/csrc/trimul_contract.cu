@@ -284,8 +284,12 @@ extern "C" int b200tri_trimul_contract(const b200tri_trimul_contract_args* a, b2
     configured[dev & 63] = true;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-  contract_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(
+  {
+    TimedLaunch timed(K_TRIMUL_CONTRACT, reinterpret_cast<cudaStream_t>(stream));
+    count_launch();
+    contract_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(
       tm_a, tm_b, p);
+  }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
 }

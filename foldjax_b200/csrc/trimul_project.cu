@@ -336,7 +336,11 @@ extern "C" int b200tri_trimul_project(const b200tri_trimul_project_args* a, b200
     configured[dev & 63] = true;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-  project_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_w, p);
+  {
+    TimedLaunch timed(K_TRIMUL_PROJECT, stream);
+    count_launch();
+    project_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_w, p);
+  }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
 }

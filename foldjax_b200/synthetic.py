@@ -1,0 +1,43 @@
+"""Seeded synthetic inputs of the benchmark's shapes (no dataset is available):
+pair tensor z ~ N(0,1), linear kernels ~ N(0, 0.02^2) in the reference's
+[in, out] layout, layer-norm scale 1 / bias 0, pad mask on the trailing tokens."""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def trimul_params(rng: np.random.Generator, c_z: int = 128, c_hidden: int = 128, std: float = 0.02) -> dict:
+    w = lambda *shape: (rng.standard_normal(shape) * std).astype(np.float32)
+    ln = lambda c: {"scale": np.ones(c, np.float32), "bias": np.zeros(c, np.float32)}
+    return {
+        "norm_in": ln(c_z), "p_in": {"kernel": w(c_z, 2 * c_hidden)}, "g_in": {"kernel": w(c_z, 2 * c_hidden)},
+        "norm_out": ln(c_hidden), "p_out": {"kernel": w(c_hidden, c_z)}, "g_out": {"kernel": w(c_z, c_z)},
+    }
+
+
+def triatt_params(rng: np.random.Generator, c_z: int = 128, heads: int = 4, head_dim: int = 32,
+                  std: float = 0.02) -> dict:
+    w = lambda *shape: (rng.standard_normal(shape) * std).astype(np.float32)
+    hd = heads * head_dim
+    return {
+        "layer_norm": {"scale": np.ones(c_z, np.float32), "bias": np.zeros(c_z, np.float32)},
+        "linear": {"kernel": w(c_z, heads)},
+        "mha": {name: {"kernel": w(c_z if name != "linear_o" else hd, hd if name != "linear_o" else c_z)}
+                for name in ("linear_q", "linear_k", "linear_v", "linear_g", "linear_o")},
+    }
+
+
+def block_params(rng: np.random.Generator) -> dict:
+    return {
+        "tri_mul_out": trimul_params(rng), "tri_mul_in": trimul_params(rng),
+        "tri_att_start": triatt_params(rng), "tri_att_end": triatt_params(rng),
+    }
+
+
+def pad_mask(n: int, n_pad: int) -> np.ndarray:
+    """[1, n, n] float32 pair mask m m^T with the last n_pad tokens dropped."""
+    m = np.ones(n, dtype=np.float32)
+    if n_pad:
+        m[n - n_pad:] = 0.0
+    return (m[:, None] * m[None, :])[None]

@@ -43,6 +43,19 @@ const char* b200tri_last_error(void);
  * >100 = the role whose bounded wait ran out) and clears it. */
 int b200tri_device_status(void);
 
+/* Measurement aids (not on the data path).
+ * b200tri_launch_count: kernels launched by this library in this process so far.
+ * b200tri_timing_enable(1): from now on the library brackets each of its main
+ *   kernels with CUDA events on the launching stream. b200tri_timing_read
+ *   synchronises the device and returns, for a kernel name ("trimul_project",
+ *   "trimul_contract", "trimul_finish", "triatt_project", "triatt_core",
+ *   "triatt_finish"), the summed duration in ms and the number of launches since
+ *   the last b200tri_timing_reset. Off by default. */
+uint64_t b200tri_launch_count(void);
+int b200tri_timing_enable(int32_t on);
+int b200tri_timing_reset(void);
+int b200tri_timing_read(const char* kernel, double* total_ms, int32_t* launches);
+
 /* ------------------------------------------------------------------------
  * Triangle multiplicative update.
  * Replaces: triangle_multiplication_forward,
