@@ -13,6 +13,7 @@ _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libb200tri.so"
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = range(6)
+TRIATT_CORE_STATIC_MAX_FLOATS = 1 << 20
 
 
 class B200TriError(RuntimeError):
@@ -154,6 +155,7 @@ SIGNATURES = {
     "b200tri_triatt_project": (C.c_int, [C.POINTER(TriattProjectArgs), C.c_void_p]),
     "b200tri_triatt_core_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200tri_triatt_core": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
+    "b200tri_triatt_core_static": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
     "b200tri_triatt_finish_workspace_bytes": (C.c_size_t, []),
     "b200tri_triatt_finish": (C.c_int, [C.POINTER(TriattFinishArgs), C.c_void_p]),
 }

@@ -69,6 +69,7 @@ int sm_count();
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
                 K_TRIATT_FINISH, K_COUNT };
 void count_launch(int n = 1);
+bool timing_enabled();
 struct TimedLaunch {  // brackets the launches made during its lifetime
   int id;
   cudaStream_t stream;

@@ -61,6 +61,8 @@ static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events[K_COUNT];
 static const char* const kKernelNames[K_COUNT] = {"trimul_project", "trimul_contract", "trimul_finish",
                                                   "triatt_project", "triatt_core",     "triatt_finish"};
 
+bool timing_enabled() { return g_timing.load(std::memory_order_relaxed) != 0; }
+
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
 TimedLaunch::TimedLaunch(int id_, cudaStream_t stream_) : id(id_), stream(stream_) {

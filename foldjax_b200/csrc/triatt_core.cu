@@ -29,6 +29,8 @@
 // 128 lanes/clk/SM that caps the tensor pipe near 25-30 % at head dim 32.
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "host.cuh"
 #include "tc.cuh"
 
@@ -487,4 +489,56 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that cannot provide scratch memory and must not allocate:
+// the mask-bias rows live in a fixed array inside the library instead of the
+// caller's workspace. Same kernel, same results as b200tri_triatt_core.
+namespace {
+
+// Host code may only use this name to ask the runtime for the device address
+// (cudaGetSymbolAddress); it is not itself a device pointer.
+// (+256 floats: the workspace carve-up of b200tri_triatt_core rounds its size up by 1 KiB)
+static __device__ __align__(256) float g_core_static_scratch[B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS + 256];
+
+// Device address of the array on the current device, looked up once per device.
+int core_static_scratch(float** out) {
+  constexpr int kMaxDev = 64;
+  static float* cache[kMaxDev] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < kMaxDev, B200TRI_ERR_CUDA, "att core static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    float* ptr = nullptr;
+    B200_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_core_static_scratch));
+    B200_REQUIRE(ptr != nullptr, B200TRI_ERR_CUDA, "att core static: no device address for the scratch array");
+    cache[dev] = ptr;
+  }
+  *out = cache[dev];
+  return B200TRI_OK;
+}
+
+}  // namespace
+
+extern "C" int b200tri_triatt_core_static(const b200tri_triatt_core_args* a, b200tri_stream_t stream) {
+  using namespace b200;
+  B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "att core static: null args");
+  B200_REQUIRE(a->n_i > 0 && a->n_k > 0, B200TRI_ERR_INVALID, "att core static: sizes must be positive");
+  const long long floats = static_cast<long long>(a->n_i) * round_up(a->n_k, 64);
+  B200_REQUIRE(floats <= B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS, B200TRI_ERR_UNSUPPORTED,
+               "att core static: n_i * round_up(n_k, 64) = %lld floats exceeds the built-in scratch of %d floats; "
+               "use b200tri_triatt_core with a workspace",
+               floats, B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS);
+  B200_REQUIRE(!timing_enabled(), B200TRI_ERR_INVALID,
+               "att core static: kernel timing is enabled (it creates CUDA events); disable it for this entry point");
+  float* scratch = nullptr;
+  int rc = core_static_scratch(&scratch);
+  if (rc) return rc;
+  b200tri_triatt_core_args local = *a;
+  local.workspace = scratch;
+  local.workspace_bytes = sizeof(float) * static_cast<size_t>(B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS + 256);
+  return b200tri_triatt_core(&local, stream);
 }

@@ -270,6 +270,34 @@ typedef struct {
 size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k);
 int b200tri_triatt_core(const b200tri_triatt_core_args* args, b200tri_stream_t stream);
 
+/* core, for callers that have no scratch memory to give and must not allocate.
+ * This entry point has no counterpart in the reference. Some hosts of this
+ * library cannot hand over a workspace: a custom-call handler inside a framework
+ * that reserved the device's memory when it started and passes the handler only
+ * the operand and result buffers it planned, or a service whose memory budget is
+ * fixed at start-up. For them cudaMalloc inside the call may fail, stall or be
+ * forbidden. This variant runs the same kernel as b200tri_triatt_core but keeps
+ * its one scratch buffer (the additive mask-bias rows, n_i x round_up(n_k, 64)
+ * floats) in a fixed array inside the library: B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS
+ * floats (4 MiB), resident on every GPU that loads the library until the process
+ * exits. `workspace` / `workspace_bytes` of the argument struct are ignored.
+ *
+ * Limits and rules:
+ *  - n_i * round_up(n_k, 64) must not exceed the maximum; larger problems are
+ *    rejected with B200TRI_ERR_UNSUPPORTED (use b200tri_triatt_core instead).
+ *  - The call allocates nothing (no cudaMalloc/cudaFree, no events): it is refused
+ *    with B200TRI_ERR_INVALID while b200tri_timing_enable(1) is in effect, because
+ *    that mode creates CUDA events.
+ *  - The first call on a device looks up the array's device address (once per
+ *    device, with that device current). Make that first call before any stream
+ *    capture begins.
+ *  - All calls on a device share the array. Every call rewrites the part it uses
+ *    before reading it, so nothing has to be cleared; but two calls whose kernels
+ *    overlap on the GPU (different streams) race on it. Keep them on one stream
+ *    or order them with events. */
+#define B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS (1 << 20)
+int b200tri_triatt_core_static(const b200tri_triatt_core_args* args, b200tri_stream_t stream);
+
 /* finish: out = bf16(bf16(o * sigmoid(LN(x) @ w_g)) @ w_o) (+ residual); x and
  * out/residual are addressed through (outer, inner) strides. */
 typedef struct {
