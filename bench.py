@@ -217,8 +217,8 @@ def run_gpu(args) -> None:
     assert torch.isfinite(result.float()).all(), "non-finite values in the block output"
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
-    e2e_steps = max(1, min(args.steps, 3))
-    for _ in range(min(args.warmup, 1)):
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    for _ in range(0 if args.no_e2e else min(args.warmup, 1)):
         triangle_block_forward(params, z_host, mask_host, out=out_host)
     barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -227,7 +227,7 @@ def run_gpu(args) -> None:
         triangle_block_forward(params, z_host, mask_host, out=out_host)
     t1.record()
     barrier()
-    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / max(e2e_steps, 1)
 
     if rank != 0:
         if world > 1:
@@ -257,7 +257,8 @@ def run_gpu(args) -> None:
             "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
         },
         "clocks": clocks,
-        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+        "e2e": None if args.no_e2e else {
+                "value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(z_host.numel() * 2 + mask_host.numel() * 4),
                 "d2h_bytes_per_step": int(out_host.numel() * 2)},
         "gpu_launches": launches,
@@ -288,6 +289,7 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=320, help="size of the bounded CPU sample")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
