@@ -9,8 +9,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libb200tri.so"
+# B200TRI_LIBRARY points at another build of the same library (kernel experiments).
+LIB_PATH = Path(os.environ.get("B200TRI_LIBRARY", _HERE / "libb200tri.so"))
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = range(6)
 TRIATT_CORE_STATIC_MAX_FLOATS = 1 << 20

@@ -3,7 +3,7 @@
 // issue/commit, TMEM loads/stores and the shared-memory operand descriptors.
 //
 // Conventions
-//  * Every wait on an mbarrier is bounded (WAIT_LIMIT_NS). When a wait gives up
+//  * Every wait on an mbarrier is bounded (WAIT_LIMIT_CYCLES). When a wait gives up
 //    it records a code in the device status word and returns false; callers
 //    leave their loops and fall through to the common tear-down, which frees
 //    TMEM. A kernel that timed out therefore returns; the host reads the status.
@@ -18,7 +18,7 @@
 
 namespace b200 {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s of SM clock per wait
 
 // Status codes written by kernels (0 = fine).
 enum : int {
@@ -84,16 +84,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. `status` points at the device status word (global memory).
-// Gives up after WAIT_LIMIT_NS, or as soon as another thread has recorded a
+// Gives up after WAIT_LIMIT_CYCLES, or as soon as another thread has recorded a
 // failure, so that one stuck role drains the whole CTA quickly.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  // Fast path: a few plain polls (the hardware parks the thread inside try_wait),
+  // no clock reads on the way.
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xff) == 0) {
+    if ((it & 0x3f) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != ST_OK) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
         atomicCAS(status, ST_OK, code);
         return false;
       }
@@ -241,6 +245,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------ helpers
@@ -274,6 +286,18 @@ __device__ __forceinline__ float sigmoid_f32(float x) { return __fdividef(1.0f, 
 __device__ __forceinline__ uint32_t sigmoid_bf16x2(float g0, float g1) {
   const uint32_t g = pack_bf16x2(g0, g1);
   return pack_bf16x2(sigmoid_f32(bf16_lo(g)), sigmoid_f32(bf16_hi(g)));
+}
+// 2^x for two packed fp16 values in one MUFU instruction.
+__device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+// max of three (one instruction on sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;

@@ -14,18 +14,20 @@
 // step, so the bias (the only operand that does not depend on i) crosses
 // L2 -> shared memory once per NWG rows.
 //
-//   warp 0        TMA producer: Q tiles per item; per 64-key step the bias tile and,
+//   warp 0        (warps 0-3 form the control warpgroup; 2 and 3 idle) TMA producer: Q tiles per item; per 64-key step the bias tile and,
 //                 per row, K [64x32], V^T [32x64] and the mask-bias row
-//   warp 1        MMA issuer: S = Q K^T (bf16, 128x64x32) into TMEM, O += P V
-//                 (fp16, 128x32x64) with P read from TMEM
+//   warp 1        Q.K^T issuer: S = Q K^T (bf16, 128x64x32) into TMEM
+//   warp 2        P.V issuer: O += P V (fp16, 128x32x64) with P read from TMEM
 //   warpgroups    softmax: one thread per query row. S from TMEM, + bias + mask,
 //                 running max with lazy rescale (the subtracted offset only moves
 //                 when the max grew by more than 2^8, so O stays in TMEM and is
 //                 rescaled rarely), exp2, row sum, P -> fp16 -> TMEM
-// TMEM per warpgroup: S 64 columns, P 32, O 32.
+// TMEM per warpgroup: S 64 columns, P 32 (fp16 pairs), O 32 + the row sum (column 128 of
+// the group; rows 32..47 of every V tile are a row of ones and zero padding, so the
+// tensor core accumulates sum_k P next to P.V).
 //
 // Bound: not the tensor pipe. Per score the SM issues ~8 ALU/MUFU instructions
-// (unpack bias, add, max, sub, mul, ex2, sum, half a cvt) against 128 tensor flops; at
+// (unpack bias, packed add, 3-input max, packed fma, ex2, packed sum, half a cvt) against 128 tensor flops; at
 // 128 lanes/clk/SM that caps the tensor pipe near 25-30 % at head dim 32.
 #include <cuda_fp16.h>
 
@@ -38,15 +40,20 @@ namespace b200 {
 
 namespace {
 
-constexpr int NWG = 4;
+#ifndef B200_NWG
+#define B200_NWG 3
+#endif
+constexpr int NWG = B200_NWG;  // softmax warpgroups = rows i that share one bias tile
 constexpr int KT = 64;
 constexpr int STAGES = 3;
-constexpr int THREADS = 64 + NWG * 128;
+constexpr int THREADS = 128 + NWG * 128;  // warpgroup 0: producer, MMA issuer, 2 idle warps; then the softmax warpgroups
 constexpr int Q_BYTES = 128 * 64;    // [128 j][32 d] bf16
 constexpr int BIAS_BYTES = 128 * 128;  // [128 j][64 k] bf16
 constexpr int K_BYTES = KT * 64;     // [64 k][32 d] bf16
-constexpr int V_BYTES = 32 * 128;    // [32 d][64 k] fp16
-constexpr uint32_t TM_S = 0, TM_P = 64, TM_O = 96, TM_WG = 128;
+constexpr int V_ROWS = 48;           // 32 head channels + a row of ones (row 32) + 15 zero rows
+constexpr int V_BYTES = V_ROWS * 128;  // [48][64 k] fp16; TMA fills rows 0..31
+constexpr int V_TMA_BYTES = 32 * 128;
+constexpr uint32_t TM_S = 0, TM_P = 64, TM_O = 96, TM_L = 128, TM_WG = 160;  // O: 32 columns + the row sum in column 128
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 5.5f;  // natural-log units, about 8 in log2
 
@@ -60,7 +67,7 @@ struct Smem {
   uint32_t tmem_base;
 };
 static_assert(sizeof(Smem) <= 232448, "shared memory budget");
-constexpr uint32_t STAGE_TX = BIAS_BYTES + NWG * (K_BYTES + V_BYTES + KT * 4);
+constexpr uint32_t STAGE_TX = BIAS_BYTES + NWG * (K_BYTES + V_TMA_BYTES + KT * 4);
 
 struct Params {
   int n_i, n_j, n_k;  // rows, queries, keys
@@ -117,6 +124,15 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
   }
+  // Rows 32..47 of every V tile are constant and never touched by TMA: row 32 is
+  // all ones, so column 32 of O accumulates the softmax row sum on the tensor core
+  // (from the very P that multiplies V); rows 33..47 are zero padding to N = 48.
+  for (int idx = threadIdx.x; idx < STAGES * NWG * (16 * 128 / 4); idx += blockDim.x) {
+    const int tile = idx / (16 * 32), w = idx % (16 * 32);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.v[0][0][0] + tile * V_BYTES + V_TMA_BYTES);
+    dst[w] = (w < 32) ? 0x3C003C00u : 0u;  // fp16 1.0 pairs in row 32
+  }
+  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -157,39 +173,55 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   } else if (warp == 1) {
+    // ---- Q.K^T issuer: S[wg] = Q[wg] . K[stage][wg]^T as soon as the warpgroup has
+    // taken the previous scores out of TMEM. Kept apart from the P.V issuer so that
+    // neither product waits behind the other's barrier; both are single threads
+    // competing with four softmax warps for issue slots on their sub-partition.
     if (elect_one()) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, KT);
-      constexpr uint32_t idesc_pv = idesc_f16(128, 32);
       int stage = 0;
       uint32_t phase = 0, item_it = 0, g = 0;  // g: global step counter
       bool alive = true;
-      auto issue_qk = [&](int wg, int st) {
-        const uint64_t adesc = desc_sw64(smem_u32(sm.q[wg]));
-        const uint64_t bdesc = desc_sw64(smem_u32(sm.k[st][wg]));
-        const uint32_t d = tmem_base + wg * TM_WG + TM_S;
-        umma_bf16_ss(d, adesc, bdesc, idesc_qk, 0);
-        umma_bf16_ss(d, umma_desc_advance(adesc, 32), umma_desc_advance(bdesc, 32), idesc_qk, 1);
-        umma_commit(&sm.s_full[wg]);
-      };
       for (long long item = blockIdx.x; item < p.total_items && alive; item += gridDim.x, ++item_it) {
         if (!mbar_wait(&sm.q_full, item_it & 1, p.status, ST_TIMEOUT_MMA)) break;
-        if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_MMA)) break;
-        tc_fence_after();
-        for (int wg = 0; wg < NWG && alive; ++wg) {
-          if (!mbar_wait(&sm.s_free[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_MMA)) {
+        for (int t = 0; t < p.steps && alive; ++t, ++g) {
+          if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_MMA)) {
             alive = false;
             break;
           }
-          tc_fence_after();
-          issue_qk(wg, stage);
-        }
-        for (int t = 0; t < p.steps && alive; ++t, ++g) {
-          int nstage = stage + 1;
-          uint32_t nphase = phase;
-          if (nstage == STAGES) {
-            nstage = 0;
-            nphase ^= 1;
+          for (int wg = 0; wg < NWG; ++wg) {
+            if (!mbar_wait(&sm.s_free[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_MMA)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t adesc = desc_sw64(smem_u32(sm.q[wg]));
+            const uint64_t bdesc = desc_sw64(smem_u32(sm.k[stage][wg]));
+            const uint32_t d = tmem_base + wg * TM_WG + TM_S;
+            umma_bf16_ss(d, adesc, bdesc, idesc_qk, 0);
+            umma_bf16_ss(d, umma_desc_advance(adesc, 32), umma_desc_advance(bdesc, 32), idesc_qk, 1);
+            umma_commit(&sm.s_full[wg]);
           }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (alive) umma_commit(&sm.q_empty);  // every Q.K^T of the item has been issued
+      }
+    }
+  } else if (warp == 2) {
+    // ---- P.V issuer: O[wg] (+)= P[wg] . V[stage][wg], P read from TMEM.
+    if (elect_one()) {
+      constexpr uint32_t idesc_pv = idesc_f16(128, V_ROWS);
+      int stage = 0;
+      uint32_t phase = 0, g = 0;
+      bool alive = true;
+      for (long long item = blockIdx.x; item < p.total_items && alive; item += gridDim.x) {
+        for (int t = 0; t < p.steps && alive; ++t, ++g) {
+          // (already complete when P arrives; observed here so this thread's products
+          // are ordered after the TMA writes of V)
+          if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_MMA)) break;
           for (int wg = 0; wg < NWG; ++wg) {
             if (!mbar_wait(&sm.p_full[wg], g & 1, p.status, ST_TIMEOUT_MMA)) {
               alive = false;
@@ -203,30 +235,21 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int k = 0; k < KT / 16; ++k)
               umma_bf16_ts(d, a + k * 8, umma_desc_advance(vdesc, k * 32), idesc_pv, (t | k) != 0);
             umma_commit(&sm.pv_done[wg]);
-            if (t + 1 < p.steps) {
-              if (wg == 0 && !mbar_wait(&sm.st_full[nstage], nphase, p.status, ST_TIMEOUT_MMA)) {
-                alive = false;
-                break;
-              }
-              if (!mbar_wait(&sm.s_free[wg], g & 1, p.status, ST_TIMEOUT_MMA)) {
-                alive = false;
-                break;
-              }
-              tc_fence_after();
-              issue_qk(wg, nstage);
-            }
           }
           if (!alive) break;
+          // K of this stage was consumed before the softmax saw its scores, V by the
+          // products just issued: the stage is free once they complete.
           umma_commit(&sm.st_empty[stage]);
-          stage = nstage;
-          phase = nphase;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
-        if (alive) umma_commit(&sm.q_empty);
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------------------------------------- softmax
-    const int wg = (warp - 2) >> 2;
+    const int wg = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // query inside the tile = TMEM lane
     const uint32_t t_wg = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + wg * TM_WG;
@@ -238,7 +261,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int rem = static_cast<int>(item % items_per_head);
       const int i = (rem / p.tiles_j) * NWG + wg;
       const int j = (rem % p.tiles_j) * 128 + row;
-      float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
+      float m_run = -INFINITY, m_used = -INFINITY;
       for (int t = 0; t < p.steps; ++t, ++g) {
         if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_SOFTMAX) ||
             !mbar_wait(&sm.s_full[wg], g & 1, p.status, ST_TIMEOUT_SOFTMAX)) {
@@ -246,33 +269,40 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
         tc_fence_after();
-        float u[KT];
+        // Scores, bias and mask travel as fp32 pairs: sm_100 adds/multiplies two
+        // fp32 values per instruction (add/fma .f32x2), halving the softmax's ALU work.
+        float2 u[KT / 2];
         {
-          uint32_t r0[32], r1[32];
-          tmem_ld32(t_wg + TM_S, r0);
-          tmem_ld32(t_wg + TM_S + 32, r1);
+          // Two halves of 32 keys: the TMEM load of the second half and the bias
+          // fetches overlap the adds of the first, and at most one raw half is live.
+          const uint8_t* brow = sm.bias[stage];
+          uint32_t r[32];
+          uint4 b4[4];
+          tmem_ld32(t_wg + TM_S, r);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) b4[c] = *reinterpret_cast<const uint4*>(brow + sw128_offset(row, c));
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            u[e] = __uint_as_float(r0[e]);
-            u[32 + e] = __uint_as_float(r1[e]);
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(&sm.s_free[wg]);
-        // + tri_bias (this thread's row of the shared tile) + mask bias (this row i)
-        const uint8_t* brow = sm.bias[stage];
+          for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 b4 = *reinterpret_cast<const uint4*>(brow + sw128_offset(row, c));
-          u[8 * c + 0] += bf16_lo(b4.x);
-          u[8 * c + 1] += bf16_hi(b4.x);
-          u[8 * c + 2] += bf16_lo(b4.y);
-          u[8 * c + 3] += bf16_hi(b4.y);
-          u[8 * c + 4] += bf16_lo(b4.z);
-          u[8 * c + 5] += bf16_hi(b4.z);
-          u[8 * c + 6] += bf16_lo(b4.w);
-          u[8 * c + 7] += bf16_hi(b4.w);
+            for (int c = 0; c < 4; ++c) {
+              const uint32_t w[4] = {b4[c].x, b4[c].y, b4[c].z, b4[c].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int q = 4 * c + e;  // pair inside this half: keys 32*half + 2q, +1
+                u[16 * half + q] = __fadd2_rn(make_float2(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1])),
+                                              make_float2(bf16_lo(w[e]), bf16_hi(w[e])));
+              }
+            }
+            if (half == 0) {
+              tmem_ld32(t_wg + TM_S + 32, r);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) b4[c] = *reinterpret_cast<const uint4*>(brow + sw128_offset(row, 4 + c));
+              tmem_ld_wait();
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&sm.s_free[wg]);
         }
         const float* mrow = sm.mb[stage][wg];
         const bool masked = __any_sync(0xffffffffu, (mrow[lane] != 0.f) || (mrow[lane + 32] != 0.f));
@@ -281,17 +311,24 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int c = 0; c < KT / 4; ++c) {
             const float4 m4 = *reinterpret_cast<const float4*>(mrow + 4 * c);
             // (q.k + mask_bias) + tri_bias in the reference; a -1e9 absorbs either order in fp32
-            u[4 * c + 0] += m4.x;
-            u[4 * c + 1] += m4.y;
-            u[4 * c + 2] += m4.z;
-            u[4 * c + 3] += m4.w;
+            u[2 * c] = __fadd2_rn(u[2 * c], make_float2(m4.x, m4.y));
+            u[2 * c + 1] = __fadd2_rn(u[2 * c + 1], make_float2(m4.z, m4.w));
+            if ((c & 3) == 3) asm volatile("" ::: "memory");  // keep the loads from piling up in registers
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.st_empty[stage]);
-        float mx = u[0];
+        // four independent chains, so the reduction is not one 32-deep dependency
+        float mxa = fmaxf(u[0].x, u[0].y), mxb = fmaxf(u[1].x, u[1].y);
+        float mxc = fmaxf(u[2].x, u[2].y), mxd = fmaxf(u[3].x, u[3].y);
 #pragma unroll
-        for (int e = 1; e < KT; ++e) mx = fmaxf(mx, u[e]);
+        for (int e = 4; e < KT / 2; e += 4) {
+          mxa = fmax3(mxa, u[e].x, u[e].y);
+          mxb = fmax3(mxb, u[e + 1].x, u[e + 1].y);
+          mxc = fmax3(mxc, u[e + 2].x, u[e + 2].y);
+          mxd = fmax3(mxd, u[e + 3].x, u[e + 3].y);
+        }
+        const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
         const float m_new = fmaxf(m_run, mx);
         m_run = m_new;
         const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
@@ -299,26 +336,36 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (need) {
           alpha = fast_exp2((m_used - m_new) * LOG2E);  // 0 on the first step (m_used = -inf)
           m_used = m_new;
-          l *= alpha;
         }
-        // exp(u - m) as exp2((u - m) * log2e): the subtraction first, so that a row
-        // whose maximum is the -1e9 mask constant (no valid key) still gets exact
-        // zeros in the exponent; folding m * log2e into an fma loses 2^-24 * 1e9.
-        uint32_t packed[KT / 2];
-#pragma unroll
-        for (int e = 0; e < KT / 2; ++e) {
-          const float p0 = fast_exp2((u[2 * e] - m_used) * LOG2E);
-          const float p1 = fast_exp2((u[2 * e + 1] - m_used) * LOG2E);
-          l += p0 + p1;
-          const __half2 h2 = __floats2half2_rn(p0, p1);
-          packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
-        }
-        // P buffer free and O stable once the previous step's P.V has completed.
+        // P buffer free and O stable once the previous step's P.V has completed (it
+        // was issued before this step's Q.K^T, so this wait does not stall).
         if (!mbar_wait(&sm.pv_done[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_SOFTMAX)) {
           alive = false;
           break;
         }
         tc_fence_after();
+        // exp(u - m) = exp2(u * log2e - m * log2e), one fma per pair. When the offset is
+        // the -1e9 mask constant (a row with no valid key so far) m * log2e cannot be
+        // held in fp32 to better than +-64, so those rows subtract first, then scale.
+        // P goes to TMEM in two halves of 32 keys to keep the live registers down.
+        const float2 log2e2 = make_float2(LOG2E, LOG2E);
+        const bool plain = m_used > -1.0e6f;
+        const float nm = plain ? -m_used * LOG2E : -m_used;
+        const float2 nm2 = make_float2(nm, nm);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float2 ue = u[16 * half + e];
+            const float2 t2 = plain ? __ffma2_rn(ue, log2e2, nm2) : __fmul2_rn(__fadd2_rn(ue, nm2), log2e2);
+            // two exponentials per MUFU instruction, in and out in fp16: the result is P
+            // in the format the tensor core reads (exponents <= 8, masked keys -> -inf -> 0)
+            const __half2 h2 = __floats2half2_rn(t2.x, t2.y);
+            packed[e] = exp2_f16x2(*reinterpret_cast<const uint32_t*>(&h2));
+          }
+          tmem_st16(t_wg + TM_P + 16 * half, packed);
+        }
         if (t > 0 && __any_sync(0xffffffffu, need)) {
           uint32_t o[32];
           tmem_ld32(t_wg + TM_O, o);
@@ -326,8 +373,13 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
           tmem_st32(t_wg + TM_O, o);
+          uint32_t lcol[16];  // the row-sum column (and its zero padding) scales the same way
+          tmem_ld16(t_wg + TM_L, lcol);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) lcol[e] = __float_as_uint(__uint_as_float(lcol[e]) * alpha);
+          tmem_st16(t_wg + TM_L, lcol);
         }
-        tmem_st32(t_wg + TM_P, packed);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&sm.p_full[wg]);
@@ -340,10 +392,12 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // ---- item epilogue: O / l -> bf16 -> o[i][j][h*32 ..]
       if (!mbar_wait(&sm.pv_done[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_SOFTMAX)) break;
       tc_fence_after();
-      uint32_t o[32];
+      uint32_t o[32], lcol[16];
       tmem_ld32(t_wg + TM_O, o);
+      tmem_ld16(t_wg + TM_L, lcol);
       tmem_ld_wait();
       tc_fence_before();
+      const float l = __uint_as_float(lcol[0]);  // sum_k exp(S - m), accumulated by the P.V products
       if (i < p.n_i && j < p.n_j) {
         const float inv = p.normalize ? __fdividef(1.0f, l) : 1.0f;
         uint4* dst = reinterpret_cast<uint4*>(p.o + (static_cast<long long>(i) * p.n_j + j) * 128 + h * 32);
