@@ -41,7 +41,17 @@ int* device_status_word() {
   return cache[dev];
 }
 
+static std::atomic<int> g_sm_limit{0};
+
+static int sm_count_device();
+
 int sm_count() {
+  const int n = sm_count_device();
+  const int lim = g_sm_limit.load(std::memory_order_relaxed);
+  return (lim > 0 && lim < n) ? lim : n;
+}
+
+static int sm_count_device() {
   constexpr int kMaxDev = 64;
   static int cache[kMaxDev] = {0};
   int dev = 0;
@@ -127,6 +137,11 @@ extern "C" {
 int b200tri_version(void) { return 100; }
 
 const char* b200tri_last_error(void) { return b200::get_error(); }
+
+int b200tri_set_sm_limit(int32_t sms) {
+  b200::g_sm_limit.store(sms > 0 ? sms : 0);
+  return B200TRI_OK;
+}
 
 uint64_t b200tri_launch_count(void) { return b200::g_launches.load(); }
 

@@ -77,7 +77,9 @@ struct Params {
   __nv_bfloat16* o;  // [n_i][n_j][128]
   float* row_max;    // optional [n_i][heads][n_j]: offset m used (natural log units)
   float* row_sum;    // optional: sum of exp(S - m)
-  int normalize;     // 1: o = O / l; 0: o = O (unnormalised, for merging across key tiles)
+  float* acc_o;      // fp32 running numerator [n_i][n_j][128] (ring attention)
+  int normalize;     // 1: write o = O / l; 0: leave the running state in acc_o/row_max/row_sum
+  int resume;        // 1: start from the running state instead of from nothing
   int* status;
 };
 
@@ -233,7 +235,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t a = tmem_base + wg * TM_WG + TM_P;
 #pragma unroll
             for (int k = 0; k < KT / 16; ++k)
-              umma_bf16_ts(d, a + k * 8, umma_desc_advance(vdesc, k * 32), idesc_pv, (t | k) != 0);
+              umma_bf16_ts(d, a + k * 8, umma_desc_advance(vdesc, k * 32), idesc_pv, (t | k | p.resume) != 0);
             umma_commit(&sm.pv_done[wg]);
           }
           if (!alive) break;
@@ -262,6 +264,38 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int i = (rem / p.tiles_j) * NWG + wg;
       const int j = (rem % p.tiles_j) * 128 + row;
       float m_run = -INFINITY, m_used = -INFINITY;
+      const bool in_range = i < p.n_i && j < p.n_j;
+      const long long si = (static_cast<long long>(i) * p.heads + h) * p.n_j + j;
+      const long long oi = (static_cast<long long>(i) * p.n_j + j) * 128 + h * 32;
+      if (p.resume) {
+        // Continue the softmax of earlier key tiles: offset, denominator and fp32
+        // numerator go back where the loop keeps them (registers and TMEM). The
+        // previous item's O has been read out by this thread already, and the
+        // first P.V of this item waits for this thread's P, so TMEM is free.
+        uint32_t o[32], lcol[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) lcol[e] = 0u;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0u;
+        if (in_range) {
+          m_used = p.row_max[si];
+          lcol[0] = __float_as_uint(p.row_sum[si]);
+          const float4* src = reinterpret_cast<const float4*>(p.acc_o + oi);
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            const float4 f = src[q4];
+            o[4 * q4 + 0] = __float_as_uint(f.x);
+            o[4 * q4 + 1] = __float_as_uint(f.y);
+            o[4 * q4 + 2] = __float_as_uint(f.z);
+            o[4 * q4 + 3] = __float_as_uint(f.w);
+          }
+        }
+        m_run = m_used;
+        tmem_st32(t_wg + TM_O, o);
+        tmem_st16(t_wg + TM_L, lcol);
+        tmem_st_wait();
+        tc_fence_before();
+      }
       for (int t = 0; t < p.steps; ++t, ++g) {
         if (!mbar_wait(&sm.st_full[stage], phase, p.status, ST_TIMEOUT_SOFTMAX) ||
             !mbar_wait(&sm.s_full[wg], g & 1, p.status, ST_TIMEOUT_SOFTMAX)) {
@@ -366,7 +400,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           tmem_st16(t_wg + TM_P + 16 * half, packed);
         }
-        if (t > 0 && __any_sync(0xffffffffu, need)) {
+        if ((t > 0 || p.resume) && __any_sync(0xffffffffu, need)) {
           uint32_t o[32];
           tmem_ld32(t_wg + TM_O, o);
           tmem_ld_wait();
@@ -398,19 +432,26 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_wait();
       tc_fence_before();
       const float l = __uint_as_float(lcol[0]);  // sum_k exp(S - m), accumulated by the P.V products
-      if (i < p.n_i && j < p.n_j) {
-        const float inv = p.normalize ? __fdividef(1.0f, l) : 1.0f;
-        uint4* dst = reinterpret_cast<uint4*>(p.o + (static_cast<long long>(i) * p.n_j + j) * 128 + h * 32);
+      if (in_range) {
+        if (p.normalize) {
+          const float inv = __fdividef(1.0f, l);
+          uint4* dst = reinterpret_cast<uint4*>(p.o + oi);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t w[4];
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = pack_bf16x2(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
-          dst[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int e = 0; e < 4; ++e)
+              w[e] = pack_bf16x2(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
+            dst[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          float4* dst = reinterpret_cast<float4*>(p.acc_o + oi);
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            dst[q4] = make_float4(__uint_as_float(o[4 * q4]), __uint_as_float(o[4 * q4 + 1]),
+                                  __uint_as_float(o[4 * q4 + 2]), __uint_as_float(o[4 * q4 + 3]));
         }
         if (p.row_max) {
-          const long long si = (static_cast<long long>(i) * p.heads + h) * p.n_j + j;
           p.row_max[si] = m_used;
           p.row_sum[si] = l;
         }
@@ -450,7 +491,8 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   using namespace b200;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "att core: null args");
-  B200_REQUIRE(a->q && a->k && a->vt && a->bias && a->o, B200TRI_ERR_INVALID, "att core: null pointer argument");
+  B200_REQUIRE(a->q && a->k && a->vt && a->bias && (a->o || a->unnormalized), B200TRI_ERR_INVALID,
+               "att core: null pointer argument");
   B200_REQUIRE(a->n_i > 0 && a->n_j > 0 && a->n_k > 0, B200TRI_ERR_INVALID, "att core: sizes must be positive");
   B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
                "att core: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
@@ -460,6 +502,9 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   B200_REQUIRE((a->row_max == nullptr) == (a->row_sum == nullptr), B200TRI_ERR_INVALID,
                "att core: row_max and row_sum go together");
   B200_REQUIRE((reinterpret_cast<uintptr_t>(a->o) & 15) == 0, B200TRI_ERR_INVALID, "att core: o must be 16-byte aligned");
+  B200_REQUIRE(!(a->unnormalized || a->resume) ||
+                   (a->acc_o && a->row_max && a->row_sum && (reinterpret_cast<uintptr_t>(a->acc_o) & 15) == 0),
+               B200TRI_ERR_INVALID, "att core: resume/unnormalized need acc_o (16-byte aligned), row_max and row_sum");
   const size_t need = b200tri_triatt_core_workspace_bytes(a->n_i, a->n_k);
   B200_REQUIRE(a->workspace && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
                "att core: workspace of %zu bytes needed", need);
@@ -525,7 +570,9 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   p.o = static_cast<__nv_bfloat16*>(a->o);
   p.row_max = a->row_max;
   p.row_sum = a->row_sum;
+  p.acc_o = a->acc_o;
   p.normalize = a->unnormalized ? 0 : 1;
+  p.resume = a->resume ? 1 : 0;
   p.status = status;
 
   static bool configured[64] = {false};

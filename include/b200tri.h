@@ -52,6 +52,10 @@ int b200tri_device_status(void);
  *   "triatt_finish"), the summed duration in ms and the number of launches since
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
+/* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
+ * them use at most n SMs (0 = all), which leaves SMs to a communication library
+ * whose kernels run beside them (NCCL send/recv during a tile exchange). */
+int b200tri_set_sm_limit(int32_t sms);
 int b200tri_timing_enable(int32_t on);
 int b200tri_timing_reset(void);
 int b200tri_timing_read(const char* kernel, double* total_ms, int32_t* launches);
@@ -245,9 +249,7 @@ int b200tri_triatt_project(const b200tri_triatt_project_args* args, b200tri_stre
  * for n_i rows, n_j queries, n_k keys (the operator the reference's attention
  * cores implement, with q pre-scaled). mask is read at mask + i*ms_i + k*ms_k,
  * NULL = ones. With row_max/row_sum not NULL the kernel also returns, per
- * (i, h, j), the offset m it subtracted and l = sum_k exp(S - m); with
- * `unnormalized` it leaves o = sum_k exp(S - m) v, so that partial results over
- * key tiles can be merged (ring attention). */
+ * (i, h, j), the offset m it subtracted and l = sum_k exp(S - m). */
 typedef struct {
   int32_t n_i, n_j, n_k, heads, head_dim;
   const void* q;  /* [n_i][n_j][128] */
@@ -265,6 +267,14 @@ typedef struct {
   int32_t unnormalized;
   void* workspace; /* b200tri_triatt_core_workspace_bytes(n_i, n_k) */
   size_t workspace_bytes;
+  /* Continuing one softmax over several key tiles (ring attention): with
+   * `unnormalized` the kernel leaves its running state - the fp32 numerator in
+   * acc_o [n_i][n_j][128], the offset in row_max and the denominator in row_sum -
+   * instead of writing o; with `resume` it starts from that state instead of from
+   * nothing. First tile: unnormalized; middle tiles: resume + unnormalized; last
+   * tile: resume only, which writes the normalised o. */
+  float* acc_o;
+  int32_t resume;
 } b200tri_triatt_core_args;
 
 size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k);

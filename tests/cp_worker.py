@@ -1,0 +1,100 @@
+"""Worker for the multi-GPU context-parallel tests (launched by torchrun).
+
+Every rank builds the same seeded full-size problem, keeps its own tile, runs the
+context-parallel op, and rank 0 gathers the tiles and compares them with the
+single-GPU kernels on the full tensor (and, at small N, with the CPU oracle).
+Exit code 0 = all comparisons passed.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def main() -> int:
+    from conftest import assert_parity
+    from foldjax_b200 import _device as dev, _lib, cp
+    from foldjax_b200.synthetic import pad_mask, triatt_params, trimul_params
+    from foldjax_b200.triangle import triangle_multiplication_forward
+    from foldjax_b200.triangle_attention import triangle_attention_forward
+
+    n = int(os.environ.get("CP_TEST_TOKENS", "512"))
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = cp.context_parallel()
+    grid = ctx.grid
+    rng = np.random.default_rng(7)
+    pm = dev.params_to_device(trimul_params(rng, std=0.05))
+    pa = dev.params_to_device(triatt_params(rng, std=0.05))
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    z_full = torch.randn(n, n, 128, generator=gen).to(torch.bfloat16).cuda()
+    mask_full = torch.from_numpy(pad_mask(n, max(1, n // 40))[0]).cuda()
+    z_tile = cp.shard_pair(ctx, z_full)
+    n_r, n_c = grid.tile_shape(n)
+    failures = 0
+
+    def gather(tile):
+        tiles = [torch.empty_like(tile) for _ in range(grid.size)] if ctx.rank == 0 else None
+        dist.gather(tile, tiles, dst=0)
+        if ctx.rank != 0:
+            return None
+        full = torch.empty(n, n, 128, dtype=tile.dtype, device=tile.device)
+        for rk, t in enumerate(tiles):
+            r, c = grid.coords(rk)
+            full[r * n_r:(r + 1) * n_r, c * n_c:(c + 1) * n_c] = t
+        return full
+
+    cases = [("trimul outgoing", lambda: cp.triangle_multiplication_cp(ctx, pm, z_tile, mask_full, "outgoing"),
+              lambda: triangle_multiplication_forward(pm, z_full, mask_full[None], "outgoing")),
+             ("trimul incoming", lambda: cp.triangle_multiplication_cp(ctx, pm, z_tile, mask_full, "incoming"),
+              lambda: triangle_multiplication_forward(pm, z_full, mask_full[None], "incoming")),
+             ("triatt starting", lambda: cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=True),
+              lambda: triangle_attention_forward(pa, z_full, mask_full[None], starting=True)),
+             ("triatt ending", lambda: cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=False),
+              lambda: triangle_attention_forward(pa, z_full, mask_full[None], starting=False))]
+    for name, run_cp, run_single in cases:
+        tile = run_cp()
+        _lib.device_status()
+        full = gather(tile)
+        if ctx.rank == 0:
+            ref = run_single()
+            _lib.device_status()
+            valid = mask_full.bool().any(dim=1)  # rows/cols with a valid key
+            ok_rows = valid[:, None, None].expand_as(ref) if "ending" not in name else valid[None, :, None].expand_as(ref)
+            if "triatt" not in name:
+                ok_rows = torch.ones_like(ref, dtype=torch.bool)
+            try:
+                info = assert_parity(ref.float().cpu().numpy(), full.float().cpu().numpy(),
+                                     where=ok_rows.cpu().numpy(), label=f"{grid.rows}x{grid.cols} {name} N={n}",
+                                     mean_tol=5e-4)
+                print(info, flush=True)
+            except AssertionError as exc:
+                failures += 1
+                print("FAILED", exc, flush=True)
+    # a second call must give the same tile (buffers are reused, transfers re-posted)
+    a = cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=True)
+    b = cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=True)
+    if not torch.equal(a, b):
+        failures += 1
+        print("FAILED: repeated call differs", flush=True)
+    flag = torch.tensor([failures], device="cuda")
+    dist.all_reduce(flag)
+    dist.destroy_process_group()
+    if ctx.rank == 0:
+        print("CP_WORKER_OK" if flag.item() == 0 else "CP_WORKER_FAILED", flush=True)
+    return int(flag.item() != 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

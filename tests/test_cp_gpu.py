@@ -1,0 +1,32 @@
+"""Multi-GPU context-parallel parity: needs at least 2 GPUs on the box; each case
+runs tests/cp_worker.py under torchrun (one process per GPU, NCCL) and checks that
+the gathered tiles equal the single-GPU kernels on the full tensor."""
+
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _run(world: int, tokens: int) -> str:
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(ROOT / "tests" / "cp_worker.py")]
+    done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert done.returncode == 0 and "CP_WORKER_OK" in done.stdout, done.stdout[-3000:] + done.stderr[-3000:]
+    return done.stdout
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 512), (4, 512), (8, 1024)])
+def test_context_parallel_matches_single_gpu(world, tokens):
+    print(_run(world, tokens))

@@ -232,3 +232,56 @@ def test_mask_none_residual_and_determinism(cuda_device):
     c = _run_forward(params, x, None, True, residual=x)
     np.testing.assert_array_equal(c, orc.round_bf16(x + a))
     assert np.array_equal(a, _run_forward(params, x, None, True))
+
+
+def test_core_resumes_across_key_tiles(cuda_device):
+    """Ring-attention building block: the same softmax continued over three key
+    tiles (running state in acc_o / row_max / row_sum) equals the one-shot core."""
+    from foldjax_b200 import _device as dev, _lib
+
+    lib = _lib.load()
+    g = torch.Generator(device="cpu").manual_seed(5)
+    n_i, n_j, h, d = 6, 200, 4, 32
+    tiles = [136, 64, 120]
+    n_k = sum(tiles)
+    ld = (n_k + 63) // 64 * 64
+    q = (torch.randn(n_i, n_j, h * d, generator=g) * 0.6).bfloat16().to(cuda_device)
+    k = (torch.randn(n_i, n_k, h * d, generator=g) * 0.6).bfloat16().to(cuda_device)
+    v = torch.randn(n_i, n_k, h * d, generator=g).bfloat16()
+    bias = (torch.randn(h, n_j, n_k, generator=g) * 3.0 + torch.linspace(-5, 5, n_k)).bfloat16()
+    mask = (torch.rand(n_i, n_k, generator=g) > 0.2).float()
+    mask[:, 0] = 1.0
+    mask[n_i - 1, :tiles[0]] = 0.0  # a row whose first key tile is fully masked
+    mask = mask.to(cuda_device)
+
+    def run(k_t, v_t, b_t, m_t, n_kt, out, **extra):
+        ldt = (n_kt + 63) // 64 * 64
+        vt = torch.zeros(n_i, h * d, ldt, dtype=torch.float16, device=cuda_device)
+        vt[:, :, :n_kt] = v_t.transpose(1, 2).to(cuda_device).half()
+        bd = torch.zeros(h, n_j, ldt, dtype=torch.bfloat16, device=cuda_device)
+        bd[:, :, :n_kt] = b_t.to(cuda_device)
+        kd = k_t.contiguous()
+        md = m_t.contiguous()
+        nb = lib.b200tri_triatt_core_workspace_bytes(n_i, n_kt)
+        ws = torch.empty(nb + 1024, dtype=torch.uint8, device=cuda_device)
+        args = _lib.TriattCoreArgs(
+            n_i=n_i, n_j=n_j, n_k=n_kt, heads=h, head_dim=d, q=q.data_ptr(), k=kd.data_ptr(), vt=vt.data_ptr(),
+            v_ld=ldt, bias=bd.data_ptr(), bias_ld=ldt, bias_head_stride=n_j * ldt, mask=md.data_ptr(), ms_i=n_kt,
+            ms_k=1, inf=1e9, o=out.data_ptr(), workspace=dev.aligned_ptr(ws), workspace_bytes=nb, **extra)
+        _lib.check(lib.b200tri_triatt_core(C.byref(args), C.c_void_p(dev.stream_ptr())))
+        torch.cuda.synchronize()
+
+    ref = torch.empty(n_i, n_j, h * d, dtype=torch.bfloat16, device=cuda_device)
+    run(k, v, bias, mask, n_k, ref, row_max=None, row_sum=None, unnormalized=0)
+    got = torch.full_like(ref, float("nan"))
+    acc = torch.zeros(n_i, n_j, h * d, dtype=torch.float32, device=cuda_device)
+    rmax = torch.zeros(n_i, h, n_j, dtype=torch.float32, device=cuda_device)
+    rsum = torch.zeros_like(rmax)
+    k0 = 0
+    for t, n_kt in enumerate(tiles):
+        sl = slice(k0, k0 + n_kt)
+        run(k[:, sl], v[:, sl], bias[:, :, sl], mask[:, sl], n_kt, got, row_max=rmax.data_ptr(),
+            row_sum=rsum.data_ptr(), acc_o=acc.data_ptr(), resume=int(t > 0), unnormalized=int(t < len(tiles) - 1))
+        k0 += n_kt
+    _lib.device_status()
+    print(assert_parity(ref.float().cpu().numpy(), got.float().cpu().numpy(), label="resumed core", mean_tol=2e-4))
