@@ -183,8 +183,8 @@ def triangle_multiplication_cp(
         blk = 128 * n_c * ld
         a_all = _bf16_buf("cp_a", m, R, 128, n_c, ld)   # slot (s, r'') <- a'_loc of (r'', r*m+s)
         b_all = _bf16_buf("cp_b", R, 128, n_c, ld)      # slot r'' <- b'_loc of (r'', c)
-        a_loc = _bf16_buf("cp_al", 1, 128, n_c, ld)
-        b_loc = b_all[r].unsqueeze(0)
+        a_loc = _bf16_buf("cp_al", 128, n_c, ld)
+        b_loc = b_all[r]
         n_outer, n_inner, xs_o, xs_i, ms_o, ms_i = n_c, n_r, 128, n_c * 128, 1, n
         msgs = trimul_incoming_msgs(grid)
         n_src, n_k = R, n_r
@@ -314,7 +314,11 @@ def triangle_attention_cp(
         rp, s = msg.slot
         return [bias_all[rp, h, s * n_c:(s + 1) * n_c] for h in range(4)]
 
-    works = _post(ctx, msgs, views)
+    # Two batches: the bias chunks (small; even the own key tile's bias may live on
+    # another rank) are needed before the first core call, the K/V tiles of the
+    # peers only before the second one.
+    _wait(_post(ctx, [msg for msg in msgs if msg.what == "bias"], views))
+    works = _post(ctx, [msg for msg in msgs if msg.what == "kv"], views)
     if grid.size > 1:
         lib.b200tri_set_sm_limit(dev_sms() - COMM_SMS)
 
