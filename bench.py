@@ -9,8 +9,9 @@ random-init N(0, 0.02) weights and a pad mask on the last ~2 % of tokens - the
 per-block work of the 48-block trunk at N = 3012 -> 3072 tokens.
 
 Prints ONE JSON line (rank 0): metric = achieved TFLOP/s over the algorithmic
-flops of the four ops, ms_per_step = block milliseconds. With N > 1 GPUs every
-rank runs its own complex (replicas, weak scaling); the value is the aggregate.
+flops of the four ops, ms_per_step = block milliseconds. With N > 1 GPUs the same
+complex is sharded over a 1x2 / 2x2 / 2x4 grid (2-D context parallelism, strong
+scaling): the value is the whole job's flops over the slowest rank's time.
 `--impl reference` times the CPU restatement of the reference's XLA path (the
 reference's JAX code cannot run here: JAX is not installed) on a bounded sample.
 """
@@ -171,16 +172,41 @@ def run_gpu(args) -> None:
     lib = _lib.load()
 
     n = args.tokens
-    rng = np.random.default_rng(3 + rank)
+    rng = np.random.default_rng(3)
     params = dev.params_to_device(make_params(rng))
     n_pad = n - int(round(n * 3012 / 3072)) if n >= 64 else 0
     mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
-    gen = torch.Generator(device="cuda").manual_seed(3 + rank)
-    z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
     mask = mask_host.cuda()
+    if world == 1:
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        run_block = lambda zz, mm: triangle_block_forward(params, zz, mm)
+        grid_name = "single GPU"
+    else:
+        # one complex sharded over an R x C grid: every rank owns one tile of z (2-D
+        # context parallelism), the whole [N, N] mask is replicated
+        from foldjax_b200 import cp
+
+        ctx = cp.context_parallel()
+        n_r, n_c = ctx.grid.tile_shape(n)
+        gen = torch.Generator(device="cuda").manual_seed(3 + rank)
+        z = torch.randn(n_r, n_c, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        mask = mask[0].contiguous()
+        mask_host = mask_host[0]
+        run_block = lambda zz, mm: cp.triangle_block_cp(ctx, params, zz, mm)
+        grid_name = f"2-D context parallel {ctx.grid.rows}x{ctx.grid.cols}, NCCL point-to-point tile exchange"
     z_host = torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True)
     z_host.copy_(z)
     out_host = torch.empty_like(z_host).pin_memory()
+
+    def run_e2e():
+        if world == 1:
+            return triangle_block_forward(params, z_host, mask_host, out=out_host)
+        zd = z_host.cuda(non_blocking=True)
+        md = mask_host.cuda(non_blocking=True)
+        out_host.copy_(run_block(zd, md), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host
 
     def barrier():
         if world > 1:
@@ -196,7 +222,7 @@ def run_gpu(args) -> None:
 
     # ---- device-resident timing (inputs already in HBM)
     for _ in range(args.warmup):
-        triangle_block_forward(params, z, mask)
+        run_block(z, mask)
     lib.b200tri_timing_reset()
     lib.b200tri_timing_enable(1)
     launches0 = lib.b200tri_launch_count()
@@ -205,7 +231,7 @@ def run_gpu(args) -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        result = triangle_block_forward(params, z, mask)
+        result = run_block(z, mask)
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
@@ -219,12 +245,12 @@ def run_gpu(args) -> None:
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
     e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 3))
     for _ in range(0 if args.no_e2e else min(args.warmup, 1)):
-        triangle_block_forward(params, z_host, mask_host, out=out_host)
+        run_e2e()
     barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(e2e_steps):
-        triangle_block_forward(params, z_host, mask_host, out=out_host)
+        run_e2e()
     t1.record()
     barrier()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / max(e2e_steps, 1)
@@ -239,28 +265,30 @@ def run_gpu(args) -> None:
     peaks, peak_kind = measured_peaks()
     core_ms, core_n = ktimes["triatt_core"]
     core_avg = core_ms / max(core_n, 1)
-    core_flops = 4.0 * n**3 * 128.0  # QK^T + PV per launch
-    achieved = core_flops / (core_avg * 1e-3) / 1e12 if core_avg else None
+    # QK^T + PV of the two attention ops of a step, this rank's share (one launch per key tile)
+    core_flops_rank = 2.0 * 4.0 * n**3 * 128.0 / world * args.steps
+    achieved = core_flops_rank / (core_ms * 1e-3) / 1e12 if core_ms else None
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
     shares = {k: round(v[0] / max(sum(t[0] for t in ktimes.values()), 1e-9), 4) for k, v in ktimes.items()}
     cores = len(os.sched_getaffinity(0))
     cpu_secs, cpu_tf = time_cpu(args.cpu_tokens, reps=1) if world == 1 and not args.no_cpu else (None, None)
     line = {
-        "metric": METRIC, "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
+        "metric": METRIC, "value": flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
                         "tri-mult out+in, tri-attn start+end, residual adds fused",
             "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops,
-            "parallelism": "single GPU" if world == 1 else f"{world} replicas, one complex per GPU, no collective",
+            "parallelism": grid_name,
             "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
         },
         "clocks": clocks,
         "e2e": None if args.no_e2e else {
-                "value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(z_host.numel() * 2 + mask_host.numel() * 4),
-                "d2h_bytes_per_step": int(out_host.numel() * 2)},
+                "value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(world * (z_host.numel() * 2 + mask_host.numel() * 4)),
+                "d2h_bytes_per_step": int(world * out_host.numel() * 2)},
         "gpu_launches": launches,
         "roofline": {
             "kernel": "att_core_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
