@@ -74,7 +74,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      // the last operand is the suspend-time hint: the hardware parks the thread until
+      // the phase completes (or this many ns pass), so a waiting warp issues almost no
+      // instructions instead of competing with the working warps of its sub-partition
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 0x989680;\n"
       " selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -286,12 +289,6 @@ __device__ __forceinline__ float sigmoid_f32(float x) { return __fdividef(1.0f, 
 __device__ __forceinline__ uint32_t sigmoid_bf16x2(float g0, float g1) {
   const uint32_t g = pack_bf16x2(g0, g1);
   return pack_bf16x2(sigmoid_f32(bf16_lo(g)), sigmoid_f32(bf16_hi(g)));
-}
-// 2^x for two packed fp16 values in one MUFU instruction.
-__device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
 }
 // max of three (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {

@@ -393,10 +393,10 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int e = 0; e < 16; ++e) {
             const float2 ue = u[16 * half + e];
             const float2 t2 = plain ? __ffma2_rn(ue, log2e2, nm2) : __fmul2_rn(__fadd2_rn(ue, nm2), log2e2);
-            // two exponentials per MUFU instruction, in and out in fp16: the result is P
-            // in the format the tensor core reads (exponents <= 8, masked keys -> -inf -> 0)
-            const __half2 h2 = __floats2half2_rn(t2.x, t2.y);
-            packed[e] = exp2_f16x2(*reinterpret_cast<const uint32_t*>(&h2));
+            // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
+            // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
+            const __half2 h2 = __floats2half2_rn(fast_exp2(t2.x), fast_exp2(t2.y));
+            packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
           }
           tmem_st16(t_wg + TM_P + 16 * half, packed);
         }

@@ -77,7 +77,7 @@ def main() -> int:
             try:
                 info = assert_parity(ref.float().cpu().numpy(), full.float().cpu().numpy(),
                                      where=ok_rows.cpu().numpy(), label=f"{grid.rows}x{grid.cols} {name} N={n}",
-                                     mean_tol=5e-4)
+                                     mean_tol=1e-3)
                 print(info, flush=True)
             except AssertionError as exc:
                 failures += 1
