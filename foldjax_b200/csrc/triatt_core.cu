@@ -56,6 +56,14 @@ constexpr int V_TMA_BYTES = 32 * 128;
 constexpr uint32_t TM_S = 0, TM_P = 64, TM_O = 96, TM_L = 128, TM_WG = 160;  // O: 32 columns + the row sum in column 128
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 5.5f;  // natural-log units, about 8 in log2
+// A dropped key's score. The reference adds -1e9 in fp32, which absorbs q.k + bias
+// (|q.k + bias| < 32 is below half an ulp of 1e9): every dropped key ends up with
+// the same score, so a row with no valid key becomes a uniform average. Here a
+// mask bias at or below MASKED_SCORE REPLACES the score with that constant, which
+// has the same two effects (zero weight beside any valid key, uniform without one)
+// while keeping the softmax offset small enough for a single fp32 fma per
+// exponent. Smaller mask biases (soft masks) are added as they are.
+constexpr float MASKED_SCORE = -30000.0f;
 
 struct Smem {
   uint8_t q[NWG][Q_BYTES];
@@ -344,9 +352,12 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int c = 0; c < KT / 4; ++c) {
             const float4 m4 = *reinterpret_cast<const float4*>(mrow + 4 * c);
-            // (q.k + mask_bias) + tri_bias in the reference; a -1e9 absorbs either order in fp32
-            u[2 * c] = __fadd2_rn(u[2 * c], make_float2(m4.x, m4.y));
-            u[2 * c + 1] = __fadd2_rn(u[2 * c + 1], make_float2(m4.z, m4.w));
+            const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
+            float uu[4] = {u[2 * c].x, u[2 * c].y, u[2 * c + 1].x, u[2 * c + 1].y};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) uu[e] = (mv[e] <= MASKED_SCORE) ? mv[e] : uu[e] + mv[e];
+            u[2 * c] = make_float2(uu[0], uu[1]);
+            u[2 * c + 1] = make_float2(uu[2], uu[3]);
             if ((c & 3) == 3) asm volatile("" ::: "memory");  // keep the loads from piling up in registers
           }
         }
@@ -378,13 +389,12 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
         tc_fence_after();
-        // exp(u - m) = exp2(u * log2e - m * log2e), one fma per pair. When the offset is
-        // the -1e9 mask constant (a row with no valid key so far) m * log2e cannot be
-        // held in fp32 to better than +-64, so those rows subtract first, then scale.
+        // exp(u - m) = exp2(u * log2e - m * log2e), one fma per pair (|m| <= 3e4, so the
+        // product m * log2e is good to 0.002 in the exponent, and exact cancellation
+        // for the keys that equal the offset).
         // P goes to TMEM in two halves of 32 keys to keep the live registers down.
         const float2 log2e2 = make_float2(LOG2E, LOG2E);
-        const bool plain = m_used > -1.0e6f;
-        const float nm = plain ? -m_used * LOG2E : -m_used;
+        const float nm = -m_used * LOG2E;
         const float2 nm2 = make_float2(nm, nm);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -392,7 +402,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const float2 ue = u[16 * half + e];
-            const float2 t2 = plain ? __ffma2_rn(ue, log2e2, nm2) : __fmul2_rn(__fadd2_rn(ue, nm2), log2e2);
+            const float2 t2 = __ffma2_rn(ue, log2e2, nm2);
             // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
             // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
             const __half2 h2 = __floats2half2_rn(fast_exp2(t2.x), fast_exp2(t2.y));
@@ -475,7 +485,7 @@ __global__ void mask_bias_kernel(const float* __restrict__ mask, long long ms_i,
   if (idx >= static_cast<long long>(n_i) * ld) return;
   const int i = static_cast<int>(idx / ld), k = static_cast<int>(idx % ld);
   float v = -INFINITY;
-  if (k < n_k) v = mask ? inf * (mask[i * ms_i + k * ms_k] - 1.0f) : 0.0f;
+  if (k < n_k) v = mask ? fmaxf(inf * (mask[i * ms_i + k * ms_k] - 1.0f), MASKED_SCORE) : 0.0f;
   out[idx] = v;
 }
 
