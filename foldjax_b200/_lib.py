@@ -61,6 +61,8 @@ class TrimulContractArgs(C.Structure):
         ("b", C.c_void_p), ("b_ld", C.c_int64), ("b_chan_stride", C.c_int64), ("b_src_stride", C.c_int64),
         ("acc_in", C.c_void_p), ("out_f32", C.c_void_p), ("out_bf16", C.c_void_p),
         ("out_ld", C.c_int64), ("out_chan_stride", C.c_int64),
+        ("a_rows_per_block", C.c_int32), ("b_rows_per_block", C.c_int32), ("out_rows_per_block", C.c_int32),
+        ("a_block_stride", C.c_int64), ("b_block_stride", C.c_int64), ("out_block_stride", C.c_int64),
     ]
 
 
@@ -75,6 +77,7 @@ class TrimulFinishArgs(C.Structure):
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("os_i", C.c_int64), ("os_j", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("t_rows_per_block", C.c_int32), ("t_block_stride", C.c_int64),
     ]
 
 

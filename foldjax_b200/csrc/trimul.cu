@@ -6,9 +6,17 @@
 
 namespace {
 
+// Intermediates are channel-major inside blocks of RPB rows: [block][128][RPB][ld].
+// A tile of the projection then stores its 128 channel planes RPB*ld*2 bytes apart
+// (384 KiB at N = 3072) instead of N*ld*2 (18 MiB), which is what its scattered
+// 256-byte stores need to run at memory speed; the contraction's TMA boxes span
+// two (a) or four (b) blocks.
+constexpr int RPB = 64;
+
 struct Plan {
-  int64_t ld;           // row pitch of the channel-major intermediates
-  int64_t chan_stride;  // elements between channels
+  int64_t ld;           // row pitch of the intermediates
+  int64_t chan_stride;  // elements between channels inside a block
+  int64_t block_stride; // elements between row blocks
   size_t inter_elems;   // elements of one intermediate (a, b or t)
   size_t off_a, off_b, off_t, off_proj, off_fin, total;
 };
@@ -18,8 +26,9 @@ struct Plan {
 static Plan plan_offsets(int32_t n) {
   Plan p;
   p.ld = b200::round_up(n, 64);
-  p.chan_stride = p.ld * n;
-  p.inter_elems = static_cast<size_t>(p.chan_stride) * 128;
+  p.chan_stride = p.ld * RPB;
+  p.block_stride = p.chan_stride * 128;
+  p.inter_elems = static_cast<size_t>(p.block_stride) * ((n + RPB - 1) / RPB);
   size_t off = 0;
   auto take = [&](size_t bytes) {
     off = (off + 1023) / 1024 * 1024;
@@ -79,8 +88,8 @@ extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stre
   pa.b = ws + pl.off_b;
   pa.ld = pl.ld;
   pa.chan_stride = pl.chan_stride;
-  pa.block_stride = 0;
-  pa.rows_per_block = a->n;
+  pa.block_stride = pl.block_stride;
+  pa.rows_per_block = RPB;
   pa.workspace = ws + pl.off_proj;
   pa.workspace_bytes = b200tri_trimul_project_workspace_bytes();
   int rc = b200tri_trimul_project(&pa, stream);
@@ -98,6 +107,8 @@ extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stre
   ca.out_bf16 = ws + pl.off_t;
   ca.out_ld = pl.ld;
   ca.out_chan_stride = pl.chan_stride;
+  ca.a_rows_per_block = ca.b_rows_per_block = ca.out_rows_per_block = RPB;
+  ca.a_block_stride = ca.b_block_stride = ca.out_block_stride = pl.block_stride;
   rc = b200tri_trimul_contract(&ca, stream);
   if (rc) return rc;
 
@@ -107,6 +118,8 @@ extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stre
   fa.t = ws + pl.off_t;
   fa.t_ld = pl.ld;
   fa.t_chan_stride = pl.chan_stride;
+  fa.t_rows_per_block = RPB;
+  fa.t_block_stride = pl.block_stride;
   fa.x = a->x;
   fa.xs_i = n * 128;
   fa.xs_j = 128;

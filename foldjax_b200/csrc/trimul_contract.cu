@@ -37,6 +37,8 @@ struct ContractParams {
   float* out_f32;
   __nv_bfloat16* out_bf16;
   long long out_ld, out_chan_stride;
+  int a_rpb, b_rpb, out_rpb;  // rows per block of the row-blocked layouts
+  long long out_block_stride;
   int* status;
 };
 
@@ -93,8 +95,9 @@ contract_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             }
             uint8_t* sa = smem + stage * STAGE_BYTES;
             mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-            tma_load_4d(sa, &tm_a, &full_bar[stage], kb * BK, mi * BM, d, s);
-            tma_load_4d(sa + A_BYTES, &tm_b, &full_bar[stage], kb * BK, nj * BN, d, s);
+            // rows are (block, row in block): a tile starts at block row0 / rpb
+            tma_load_5d(sa, &tm_a, &full_bar[stage], kb * BK, (mi * BM) % p.a_rpb, (mi * BM) / p.a_rpb, d, s);
+            tma_load_5d(sa + A_BYTES, &tm_b, &full_bar[stage], kb * BK, (nj * BN) % p.b_rpb, (nj * BN) / p.b_rpb, d, s);
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1;
@@ -148,7 +151,9 @@ contract_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const int row = mi * BM + quarter * 32 + lane;
-      const long long row_off = static_cast<long long>(d) * p.out_chan_stride + static_cast<long long>(row) * p.out_ld;
+      const long long row_off = static_cast<long long>(row / p.out_rpb) * p.out_block_stride +
+                                static_cast<long long>(d) * p.out_chan_stride +
+                                static_cast<long long>(row % p.out_rpb) * p.out_ld;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {
@@ -244,21 +249,48 @@ extern "C" int b200tri_trimul_contract(const b200tri_trimul_contract_args* a, b2
   int* status = device_status_word();
   B200_REQUIRE(status != nullptr, B200TRI_ERR_CUDA, "contract: no current CUDA device");
 
+  // Row-blocked operands: rows_per_block 0 (or >= the row count) means one block.
+  // A blocked operand needs blocks that tile the kernel's 128- / 256-row tiles.
+  auto blocking = [](int32_t rpb, int32_t n, int tile, int* rows, uint32_t* box_r, uint32_t* box_b, uint64_t* blocks) {
+    if (rpb <= 0 || rpb >= n) {
+      *rows = n;
+      *box_r = static_cast<uint32_t>(tile);
+      *box_b = 1;
+      *blocks = 1;
+      return true;
+    }
+    if (rpb % tile != 0 && tile % rpb != 0) return false;
+    *rows = rpb;
+    *box_r = static_cast<uint32_t>(rpb < tile ? rpb : tile);
+    *box_b = static_cast<uint32_t>(tile / static_cast<int>(*box_r));
+    *blocks = static_cast<uint64_t>((n + rpb - 1) / rpb);
+    return true;
+  };
+  int a_rows, b_rows;
+  uint32_t a_box_r, a_box_b, b_box_r, b_box_b;
+  uint64_t a_blocks, b_blocks;
+  B200_REQUIRE(blocking(a->a_rows_per_block, a->n_i, BM, &a_rows, &a_box_r, &a_box_b, &a_blocks) &&
+                   blocking(a->b_rows_per_block, a->n_j, BN, &b_rows, &b_box_r, &b_box_b, &b_blocks),
+               B200TRI_ERR_INVALID, "contract: rows_per_block must divide or be a multiple of the tile rows (128 for a, 256 for b)");
+  B200_REQUIRE(a->a_block_stride % 8 == 0 && a->b_block_stride % 8 == 0 && a->out_block_stride % 8 == 0,
+               B200TRI_ERR_INVALID, "contract: block strides must be multiples of 8 elements");
   CUtensorMap tm_a, tm_b;
   {
-    const uint64_t dims[4] = {(uint64_t)a->n_k, (uint64_t)a->n_i, 128, (uint64_t)a->n_src};
-    const uint64_t str[3] = {(uint64_t)a->a_ld * 2, (uint64_t)a->a_chan_stride * 2,
+    const uint64_t dims[5] = {(uint64_t)a->n_k, (uint64_t)a_rows, a_blocks, 128, (uint64_t)a->n_src};
+    const uint64_t str[4] = {(uint64_t)a->a_ld * 2, (uint64_t)(a_blocks > 1 ? a->a_block_stride : a->a_chan_stride * 128) * 2,
+                             (uint64_t)a->a_chan_stride * 2,
                              (uint64_t)(a->n_src > 1 ? a->a_src_stride : a->a_chan_stride * 128) * 2};
-    const uint32_t box[4] = {BK, BM, 1, 1};
-    int rc = make_tmap(&tm_a, a->a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, str, box, Swz::B128);
+    const uint32_t box[5] = {BK, a_box_r, a_box_b, 1, 1};
+    int rc = make_tmap(&tm_a, a->a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, dims, str, box, Swz::B128);
     if (rc) return rc;
   }
   {
-    const uint64_t dims[4] = {(uint64_t)a->n_k, (uint64_t)a->n_j, 128, (uint64_t)a->n_src};
-    const uint64_t str[3] = {(uint64_t)a->b_ld * 2, (uint64_t)a->b_chan_stride * 2,
+    const uint64_t dims[5] = {(uint64_t)a->n_k, (uint64_t)b_rows, b_blocks, 128, (uint64_t)a->n_src};
+    const uint64_t str[4] = {(uint64_t)a->b_ld * 2, (uint64_t)(b_blocks > 1 ? a->b_block_stride : a->b_chan_stride * 128) * 2,
+                             (uint64_t)a->b_chan_stride * 2,
                              (uint64_t)(a->n_src > 1 ? a->b_src_stride : a->b_chan_stride * 128) * 2};
-    const uint32_t box[4] = {BK, BN, 1, 1};
-    int rc = make_tmap(&tm_b, a->b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, str, box, Swz::B128);
+    const uint32_t box[5] = {BK, b_box_r, b_box_b, 1, 1};
+    int rc = make_tmap(&tm_b, a->b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, dims, str, box, Swz::B128);
     if (rc) return rc;
   }
   ContractParams p;
@@ -274,6 +306,10 @@ extern "C" int b200tri_trimul_contract(const b200tri_trimul_contract_args* a, b2
   p.out_bf16 = static_cast<__nv_bfloat16*>(a->out_bf16);
   p.out_ld = a->out_ld;
   p.out_chan_stride = a->out_chan_stride;
+  p.a_rpb = a_rows;
+  p.b_rpb = b_rows;
+  p.out_rpb = (a->out_rows_per_block > 0 && a->out_rows_per_block < a->n_i) ? a->out_rows_per_block : (a->n_i > 0 ? a->n_i : 1);
+  p.out_block_stride = a->out_block_stride;
   p.status = status;
 
   static bool configured[64] = {false};

@@ -49,6 +49,7 @@ struct FinishParams {
   __nv_bfloat16* out;
   long long os_i, os_j;
   float eps;
+  int t_rpb;  // rows per block of t
   int* status;
 };
 
@@ -111,7 +112,7 @@ finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         mbar_expect_tx(&sm.in_full[stage], 2 * TILE_BYTES);
         tma_load_3d(sm.x[stage], &tm_x, &sm.in_full[stage], 0, j0, i);
         tma_load_3d(sm.x[stage] + SLAB_BYTES, &tm_x, &sm.in_full[stage], 64, j0, i);
-        tma_load_3d(sm.t[stage], &tm_t, &sm.in_full[stage], j0, i, 0);
+        tma_load_4d(sm.t[stage], &tm_t, &sm.in_full[stage], j0, i % p.t_rpb, 0, i / p.t_rpb);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -280,10 +281,16 @@ extern "C" int b200tri_trimul_finish(const b200tri_trimul_finish_args* a, b200tr
     if (rc) return rc;
   }
   {
-    const uint64_t dims[3] = {(uint64_t)a->n_j, (uint64_t)a->n_i, 128};
-    const uint64_t str[2] = {(uint64_t)a->t_ld * 2, (uint64_t)a->t_chan_stride * 2};
-    const uint32_t box[3] = {128, 1, 128};
-    int rc = make_tmap(&tm_t, a->t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::None);
+    // (j, row in block, channel, block); one block when t is not row-blocked
+    const bool blocked = a->t_rows_per_block > 0 && a->t_rows_per_block < a->n_i;
+    const uint64_t rpb = blocked ? (uint64_t)a->t_rows_per_block : (uint64_t)a->n_i;
+    const uint64_t blocks = (a->n_i + rpb - 1) / rpb;
+    B200_REQUIRE(!blocked || a->t_block_stride % 8 == 0, B200TRI_ERR_INVALID, "finish: t_block_stride must be a multiple of 8");
+    const uint64_t dims[4] = {(uint64_t)a->n_j, rpb, 128, blocks};
+    const uint64_t str[3] = {(uint64_t)a->t_ld * 2, (uint64_t)a->t_chan_stride * 2,
+                             (uint64_t)(blocked ? a->t_block_stride : a->t_chan_stride * 128) * 2};
+    const uint32_t box[4] = {128, 1, 128, 1};
+    int rc = make_tmap(&tm_t, a->t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, str, box, Swz::None);
     if (rc) return rc;
   }
   {
@@ -304,6 +311,7 @@ extern "C" int b200tri_trimul_finish(const b200tri_trimul_finish_args* a, b200tr
   p.os_i = a->os_i;
   p.os_j = a->os_j;
   p.eps = a->eps;
+  p.t_rpb = (a->t_rows_per_block > 0 && a->t_rows_per_block < a->n_i) ? a->t_rows_per_block : a->n_i;
   p.status = status;
 
   static bool configured[64] = {false};

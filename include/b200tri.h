@@ -144,6 +144,13 @@ typedef struct {
   float* out_f32;
   void* out_bf16;
   int64_t out_ld, out_chan_stride;
+  /* Optional row blocking (0 = one block): row i of an operand lives at
+   * (i / rows_per_block) * block_stride + d * chan_stride + (i % rows_per_block) * ld.
+   * Blocks keep the 128 channel planes of a tile close together in memory, which is
+   * what the projection stage's stores want. a needs rows_per_block dividing or a
+   * multiple of 128, b of 256. */
+  int32_t a_rows_per_block, b_rows_per_block, out_rows_per_block;
+  int64_t a_block_stride, b_block_stride, out_block_stride;
 } b200tri_trimul_contract_args;
 
 int b200tri_trimul_contract(const b200tri_trimul_contract_args* args, b200tri_stream_t stream);
@@ -168,6 +175,8 @@ typedef struct {
   int64_t os_i, os_j; /* element strides of out / residual */
   void* workspace;
   size_t workspace_bytes;
+  int32_t t_rows_per_block; /* optional row blocking of t (0 = one block), as in contract */
+  int64_t t_block_stride;
 } b200tri_trimul_finish_args;
 
 size_t b200tri_trimul_finish_workspace_bytes(void);
