@@ -43,6 +43,9 @@ namespace {
 #ifndef B200_NWG
 #define B200_NWG 3
 #endif
+#ifndef B200_TURNS
+#define B200_TURNS 1
+#endif
 constexpr int NWG = B200_NWG;  // softmax warpgroups = rows i that share one bias tile
 constexpr int KT = 64;
 constexpr int STAGES = 3;
@@ -72,6 +75,7 @@ struct Smem {
   uint8_t v[STAGES][NWG][V_BYTES];
   float mb[STAGES][NWG][KT];
   uint64_t q_full, q_empty, st_full[STAGES], st_empty[STAGES], s_full[NWG], s_free[NWG], p_full[NWG], pv_done[NWG];
+  uint64_t turn[NWG][4];  // whose exponentials run on each scheduler's MUFU unit
   uint32_t tmem_base;
 };
 static_assert(sizeof(Smem) <= 232448, "shared memory budget");
@@ -127,6 +131,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.s_free[g], 128);
       mbar_init(&sm.p_full[g], 128);
       mbar_init(&sm.pv_done[g], 1);
+      for (int qr = 0; qr < 4; ++qr) mbar_init(&sm.turn[g][qr], 1);
     }
     fence_barrier_init();
   }
@@ -389,6 +394,18 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
         tc_fence_after();
+#if B200_TURNS
+        // The exponentials of one warp keep a scheduler's MUFU unit busy by themselves,
+        // while the rest of a step (loads, adds, maxima) needs issue slots but no MUFU.
+        // Left alone, the three warps of a scheduler drift into the same phase and the
+        // two resources are used one after the other. So the exponent phase is taken in
+        // turns: warpgroup w runs it after warpgroup w - 1 (warpgroup 0 after the last
+        // one's previous step), and the others' load/add/max work fills the issue slots.
+        if (!mbar_wait(&sm.turn[wg][quarter], wg == 0 ? ((g & 1) ^ 1) : (g & 1), p.status, ST_TIMEOUT_SOFTMAX)) {
+          alive = false;
+          break;
+        }
+#endif
         // exp(u - m) = exp2(u * log2e - m * log2e), one fma per pair (|m| <= 3e4, so the
         // product m * log2e is good to 0.002 in the exponent, and exact cancellation
         // for the keys that equal the offset).
@@ -410,6 +427,10 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           tmem_st16(t_wg + TM_P + 16 * half, packed);
         }
+#if B200_TURNS
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.turn[(wg + 1) % NWG][quarter]);
+#endif
         if ((t > 0 || p.resume) && __any_sync(0xffffffffu, need)) {
           uint32_t o[32];
           tmem_ld32(t_wg + TM_O, o);
