@@ -316,6 +316,8 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
         tc_fence_after();
+        // (fetched here, long before the vote that needs them)
+        const float mk0 = sm.mb[stage][wg][lane], mk1 = sm.mb[stage][wg][lane + 32];
         // Scores, bias and mask travel as fp32 pairs: sm_100 adds/multiplies two
         // fp32 values per instruction (add/fma .f32x2), halving the softmax's ALU work.
         float2 u[KT / 2];
@@ -352,7 +354,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mbar_arrive(&sm.s_free[wg]);
         }
         const float* mrow = sm.mb[stage][wg];
-        const bool masked = __any_sync(0xffffffffu, (mrow[lane] != 0.f) || (mrow[lane + 32] != 0.f));
+        const bool masked = __any_sync(0xffffffffu, (mk0 != 0.f) || (mk1 != 0.f));
         if (masked) {
 #pragma unroll
           for (int c = 0; c < KT / 4; ++c) {
