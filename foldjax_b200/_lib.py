@@ -128,6 +128,16 @@ class TriattFinishArgs(C.Structure):
     ]
 
 
+class PairTransitionArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int64), ("channels", C.c_int32), ("hidden", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p),
+        ("fc1", C.c_void_p), ("fc2", C.c_void_p), ("fc3", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 # C struct name -> ctypes mirror (tests compare sizeof on both sides)
 STRUCTS = {
     "b200tri_trimul_args": TrimulArgs,
@@ -138,6 +148,7 @@ STRUCTS = {
     "b200tri_triatt_project_args": TriattProjectArgs,
     "b200tri_triatt_core_args": TriattCoreArgs,
     "b200tri_triatt_finish_args": TriattFinishArgs,
+    "b200tri_pair_transition_args": PairTransitionArgs,
 }
 
 # name -> (restype, argtypes); every symbol include/b200tri.h declares.
@@ -166,6 +177,8 @@ SIGNATURES = {
     "b200tri_triatt_core_static": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
     "b200tri_triatt_finish_workspace_bytes": (C.c_size_t, []),
     "b200tri_triatt_finish": (C.c_int, [C.POINTER(TriattFinishArgs), C.c_void_p]),
+    "b200tri_pair_transition_workspace_bytes": (C.c_size_t, [C.c_int32]),
+    "b200tri_pair_transition": (C.c_int, [C.POINTER(PairTransitionArgs), C.c_void_p]),
 }
 
 _lib = None
@@ -205,7 +218,8 @@ def device_status() -> int:
     return st
 
 
-KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish")
+KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish",
+           "pair_transition")
 
 
 def kernel_times() -> dict[str, tuple[float, int]]:

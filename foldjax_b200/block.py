@@ -1,14 +1,17 @@
-"""The triangle path of one Pairformer block: the four pair updates in the
-reference's order, each with its residual add fused into the kernel.
+"""The pair track of one Pairformer block: the four triangle updates and the pair
+transition in the reference's order, each with its residual add fused into the
+kernel.
 
 Mirrors the pair-stack part of ``pairformer_layer_forward``
-(src/foldjax/models/boltz2/models/trunk_blocks/pairformer.py:126-150):
+(src/foldjax/models/boltz2/models/trunk_blocks/pairformer.py:126-180):
 
     z = z + tri_mul_out(z);  z = z + tri_mul_in(z)
     z = z + tri_att_start(z);  z = z + tri_att_end(z)
+    z = z + transition_z(z)
 
 ``params`` uses the reference's names for these sub-modules: ``tri_mul_out``,
-``tri_mul_in``, ``tri_att_start``, ``tri_att_end``.
+``tri_mul_in``, ``tri_att_start``, ``tri_att_end`` and (optional) ``transition_z``;
+without the last key only the four triangle updates run.
 """
 
 from __future__ import annotations
@@ -19,6 +22,7 @@ import numpy as np
 import torch
 
 from . import _device as dev
+from .transition import transition_forward
 from .triangle import triangle_multiplication_forward
 from .triangle_attention import triangle_attention_forward
 
@@ -30,8 +34,14 @@ def block_flops(n: int) -> float:
     return 2.0 * (256.0 * n**3 + 196608.0 * n**2) + 2.0 * (512.0 * n**3 + 164864.0 * n**2)
 
 
+def transition_flops(n: int, c_z: int = 128, hidden: int = 512) -> float:
+    """Algorithmic flops of the pair transition: three c_z x hidden products per pair."""
+    return 2.0 * n * n * 3 * c_z * hidden
+
+
 def triangle_block_forward(params: Mapping[str, Any], z: Any, mask: Any | None, *, out: Any | None = None):
-    """Apply the four triangle updates of one block to the pair tensor.
+    """Apply the four triangle updates (and the pair transition, if ``params`` has
+    ``transition_z``) of one block to the pair tensor.
 
     Device tensors: ``z`` is updated out of place and the new pair tensor is
     returned (``out`` may alias nothing). Host tensors (NumPy arrays or CPU torch
@@ -54,6 +64,8 @@ def triangle_block_forward(params: Mapping[str, Any], z: Any, mask: Any | None, 
         else:
             triangle_attention_forward(params[name], cur, md, starting=name.endswith("start"), residual=cur, out=nxt)
         cur = nxt
+    if "transition_z" in params:
+        transition_forward(params["transition_z"], cur, residual=cur, out=cur)  # row-local: safe in place
     if not host_in:
         return cur
     if out is None:

@@ -49,7 +49,7 @@ int b200tri_device_status(void);
  *   kernels with CUDA events on the launching stream. b200tri_timing_read
  *   synchronises the device and returns, for a kernel name ("trimul_project",
  *   "trimul_contract", "trimul_finish", "triatt_project", "triatt_core",
- *   "triatt_finish"), the summed duration in ms and the number of launches since
+ *   "triatt_finish", "pair_transition"), the summed duration in ms and the number of launches since
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
 /* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
@@ -338,6 +338,38 @@ typedef struct {
 
 size_t b200tri_triatt_finish_workspace_bytes(void);
 int b200tri_triatt_finish(const b200tri_triatt_finish_args* args, b200tri_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Pair transition (the feed-forward that follows the triangle ops in a
+ * Pairformer block).
+ * Replaces: transition_forward,
+ *   src/foldjax/models/boltz2/models/primitives/transition.py:41-127, as called
+ *   on the pair tensor by src/foldjax/models/boltz2/models/pairformer.py:152-160
+ *   (and its fused-GLU branch, glu_backend="tokamax", :101-105).
+ * Computes  update = (silu(LN(x) @ fc1) * (LN(x) @ fc2)) @ fc3  per row of the
+ * flattened [rows][128] tensor, with the reference's bf16 rounding points.
+ * The op is row-local, so a context-parallel caller passes its own tile.
+ * If `residual` is not NULL the kernel writes residual + update; residual may
+ * alias x and out (the block's z += transition(z)). */
+typedef struct {
+  int64_t rows;          /* pairs: product of all leading axes */
+  int32_t channels;      /* 128 */
+  int32_t hidden;        /* width of fc1/fc2 outputs: a multiple of 64 (512 in the Pairformer) */
+  float eps;
+  const void* x;         /* bf16 [rows][128], contiguous */
+  const void* norm_scale;
+  const void* norm_bias; /* bf16 [128] */
+  const void* fc1;       /* bf16 [128][hidden]  ([in, out], the reference's layout) */
+  const void* fc2;       /* bf16 [128][hidden] */
+  const void* fc3;       /* bf16 [hidden][128] */
+  const void* residual;  /* bf16 [rows][128] or NULL */
+  void* out;             /* bf16 [rows][128] */
+  void* workspace;
+  size_t workspace_bytes;
+} b200tri_pair_transition_args;
+
+size_t b200tri_pair_transition_workspace_bytes(int32_t hidden);
+int b200tri_pair_transition(const b200tri_pair_transition_args* args, b200tri_stream_t stream);
 
 #ifdef __cplusplus
 }

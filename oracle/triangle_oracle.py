@@ -12,6 +12,7 @@ It restates, in plain NumPy, the arithmetic of the reference's XLA (jnp) path
 * sigmoid GLU .......... src/foldjax/models/boltz2/models/primitives/glu_backend.py:36-37
 * triangle multiplication  src/foldjax/models/boltz2/models/triangle/triangle.py:78-129, 227-241
 * triangle attention ... src/foldjax/models/boltz2/models/triangle/triangle_attention.py:125-162, 346-455
+* pair transition ...... src/foldjax/models/boltz2/models/primitives/transition.py:99-112
 
 The arithmetic itself lives in a dependency that is not vendored in the
 reference: jax / jaxlib 0.10.1 (uv.lock), i.e. XLA's dot, softmax, sigmoid and
@@ -24,6 +25,8 @@ tests/models/boltz2/test_triangle_attention_checkpoint_parity.py:94-147).
 ``tests/golden/make_golden.py`` imports those test helpers from the reference
 checkout and runs them on seeded inputs; the outputs are committed as
 ``tests/golden/*.npz`` and ``tests/test_oracle.py`` holds this oracle to them.
+The transition is pinned the same way by the ``TorchTransition`` module of
+tests/models/boltz2/test_transition_forward.py:11-33 (1e-5).
 
 Two precisions are offered by every function:
 
@@ -246,6 +249,39 @@ def triangle_attention(
     if return_parts:
         return out, {"q": q, "k": k, "v": v, "tri_bias": tri_bias, "mask_bias": mask_bias, "gate": g}
     return out
+
+
+# ------------------------------------------------------------- pair transition
+def transition(params: Params, x: np.ndarray, eps: float = 1e-5, dtype: str = "float64") -> np.ndarray:
+    """transition.py:99-112 (the unchunked XLA branch): LN, one matmul against
+    concat(fc1, fc2), silu(first half) * second half, matmul against fc3.
+    x [..., C] -> update [..., C] (the caller adds the residual,
+    pairformer.py:152-160). In bf16 the matmul outputs, the sigmoid and both
+    products are each rounded to the trunk dtype."""
+    pr = _Prec(dtype)
+    xn = layer_norm(x, params["norm"]["scale"], params["norm"]["bias"], eps, dtype)  # :99
+    a = _linear(xn, params["fc1"]["kernel"], pr)  # :108-109
+    b = _linear(xn, params["fc2"]["kernel"], pr)
+    silu = pr.r(a * pr.r(_sigmoid(a)))  # jax.nn.silu = x * sigmoid(x)  :110
+    hidden = pr.r(silu * b)
+    return _linear(hidden, params["fc3"]["kernel"], pr)  # :111
+
+
+def random_transition_params(rng: np.random.Generator, c_z: int = 128, expansion: int = 4, std: float = 0.02,
+                             ln_noise: float = 0.0) -> dict:
+    def w(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    hidden = expansion * c_z
+    return {
+        "norm": {
+            "scale": (1.0 + ln_noise * rng.standard_normal(c_z)).astype(np.float32),
+            "bias": (ln_noise * rng.standard_normal(c_z)).astype(np.float32),
+        },
+        "fc1": {"kernel": w(c_z, hidden)},
+        "fc2": {"kernel": w(c_z, hidden)},
+        "fc3": {"kernel": w(hidden, c_z)},
+    }
 
 
 # ------------------------------------------------------------ synthetic inputs

@@ -55,6 +55,18 @@ def load_triatt_golden(name: str):
     return params, g["x"], g["mask"], outs
 
 
+def load_transition_golden(name: str):
+    """Golden case -> (params in the reference's [in,out] layout, x, outputs)."""
+    g = np.load(GOLDEN / name)
+    params = {
+        "norm": {"scale": g["w.norm.weight"], "bias": g["w.norm.bias"]},
+        "fc1": {"kernel": _t(g["w.fc1.weight"])},
+        "fc2": {"kernel": _t(g["w.fc2.weight"])},
+        "fc3": {"kernel": _t(g["w.fc3.weight"])},
+    }
+    return params, g["x"], {"whole": g["out"], "chunked": g["out.chunked"]}
+
+
 @pytest.fixture(scope="session")
 def cuda_device():
     torch = pytest.importorskip("torch")

@@ -14,7 +14,11 @@ equal to its jnp path within 2e-4 / 3e-4:
 * tests/models/boltz2/test_triangle_attention_checkpoint_parity.py
     ``_torch_triangle_attention_forward`` / ``_torch_mha`` (lines 94-147)
 
-This script imports those two test modules from the checkout *unmodified* (JAX
+and a PyTorch module for the pair transition, asserted equal to 1e-5:
+
+* tests/models/boltz2/test_transition_forward.py ``TorchTransition`` (lines 11-33)
+
+This script imports those test modules from the checkout *unmodified* (JAX
 and the FoldJAX package, which the modules import at the top but the helpers do
 not touch, are replaced by empty stand-ins), runs the helpers on seeded random
 inputs and weights, and stores inputs, weights and outputs in ``*.npz`` next to
@@ -54,7 +58,9 @@ def _load_reference_test(rel: str):
         _stub(name)
     sys.modules["jax"].numpy = sys.modules["jax.numpy"]
     _stub("foldjax.models.boltz2.bridge.torch_mapping", map_triangle_multiplication_state_dict=None,
-          map_triangle_attention_state_dict=None)
+          map_triangle_attention_state_dict=None, map_transition_state_dict=None)
+    _stub("foldjax.models.boltz2.models.primitives")
+    _stub("foldjax.models.boltz2.models.primitives.transition", transition_forward=None)
     _stub("foldjax.models.boltz2.models.triangle.triangle", triangle_multiplication_forward=None)
     _stub("foldjax.models.boltz2.models.triangle.triangle_attention", triangle_attention_forward=None)
     _stub("tests.models.boltz2.torch_checkpoint", load_torch_checkpoint_state_dict=None)
@@ -128,6 +134,20 @@ def make_triatt(mod, seed: int, n: int, c: int, heads: int, hidden: int, keep: f
     return out
 
 
+def make_transition(mod, seed: int, rows: tuple[int, ...], dim: int, hidden: int) -> dict:
+    torch.manual_seed(seed)
+    module = mod.TorchTransition(dim=dim, hidden_dim=hidden).eval()
+    gen = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        module.norm.weight.copy_(1.0 + _w(gen, dim))
+        module.norm.bias.copy_(_w(gen, dim))
+        x = torch.randn(*rows, dim, generator=gen, dtype=torch.float32)
+        out = {"x": x.numpy(), "out": module(x).numpy(), "out.chunked": module(x, chunk_size=max(1, hidden // 3)).numpy()}
+    for key, val in module.state_dict().items():  # torch [out, in] layout
+        out["w." + key] = val.detach().numpy()
+    return out
+
+
 def main() -> None:
     torch.manual_seed(0)
     tm = _load_reference_test("tests/models/boltz2/test_triangle_checkpoint_parity.py")
@@ -138,6 +158,9 @@ def main() -> None:
     np.savez_compressed(OUT / "triatt_n7_c8.npz", **make_triatt(ta, 13, n=7, c=8, heads=2, hidden=4, keep=0.8, pad=0))
     np.savez_compressed(OUT / "triatt_n12_c128.npz",
                         **make_triatt(ta, 14, n=12, c=128, heads=4, hidden=32, keep=0.85, pad=2))
+    tr = _load_reference_test("tests/models/boltz2/test_transition_forward.py")
+    np.savez_compressed(OUT / "transition_d5_h11.npz", **make_transition(tr, 15, rows=(2, 3), dim=5, hidden=11))
+    np.savez_compressed(OUT / "transition_d128_h512.npz", **make_transition(tr, 16, rows=(3, 8), dim=128, hidden=512))
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 
