@@ -255,6 +255,24 @@ def run_gpu(args) -> None:
     barrier()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / max(e2e_steps, 1)
 
+    # ---- the pair transition that follows the triangle ops in the block (row-local, so
+    # every rank runs it on its own tile); reported beside the headline, not inside it
+    from foldjax_b200.synthetic import transition_params
+    from foldjax_b200.transition import transition_forward
+
+    tparams = dev.params_to_device(transition_params(np.random.default_rng(4)))
+    tz, tout = (z if world > 1 else z[0]), torch.empty_like(z if world > 1 else z[0])
+    for _ in range(2):
+        transition_forward(tparams, tz, residual=tz, out=tout)
+    barrier()
+    t0.record()
+    for _ in range(4):
+        transition_forward(tparams, tz, residual=tz, out=tout)
+    t1.record()
+    barrier()
+    transition_ms = max_over_ranks(t0.elapsed_time(t1)) / 4
+    del tout
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -298,6 +316,10 @@ def run_gpu(args) -> None:
             "traffic": 1.907e9 if (n == 1024 and world == 1) else None, "avg_launch_ms": core_avg, "launches": core_n,
             "note": "binding resource is the MUFU/ALU softmax path (4*N^3 exps), not the tensor pipe",
         },
+        "pair_transition": {
+            "ms": transition_ms, "tflops": 2.0 * n * n * 3 * 128 * 512 / (transition_ms * 1e-3) / 1e12,
+            "gbs": 3.0 * n * n * 256 / world / (transition_ms * 1e-3) / 1e9,
+            "note": "LN + SwiGLU 128->512->128 + residual, one kernel; not part of `value`"},
         "kernel_ms_per_launch": {k: round(v[0] / max(v[1], 1), 4) for k, v in ktimes.items()},
         "kernel_time_share": shares,
         "cpu_baseline": None if cpu_tf is None else {

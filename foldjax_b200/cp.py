@@ -363,8 +363,10 @@ def triangle_attention_cp(
 
 
 def triangle_block_cp(ctx: CPContext, params: Mapping[str, Any], z: torch.Tensor, mask: torch.Tensor | None):
-    """The four triangle updates of one Pairformer block on this rank's tile, residual
-    adds fused (pairformer.py:126-150 under the 2-D layout)."""
+    """The pair track of one Pairformer block on this rank's tile, residual adds fused
+    (pairformer.py:126-180 under the 2-D layout): the four triangle updates, then the
+    pair transition if ``params`` has ``transition_z`` (row-local, so it needs no
+    exchange)."""
     work = (torch.empty_like(z), torch.empty_like(z))
     cur = z
     for step, name in enumerate(("tri_mul_out", "tri_mul_in", "tri_att_start", "tri_att_end")):
@@ -375,4 +377,8 @@ def triangle_block_cp(ctx: CPContext, params: Mapping[str, Any], z: torch.Tensor
         else:
             triangle_attention_cp(ctx, params[name], cur, mask, starting=name.endswith("start"), residual=cur, out=nxt)
         cur = nxt
+    if "transition_z" in params:
+        from .transition import transition_forward
+
+        transition_forward(params["transition_z"], cur, residual=cur, out=cur)
     return cur

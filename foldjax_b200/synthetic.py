@@ -28,11 +28,24 @@ def triatt_params(rng: np.random.Generator, c_z: int = 128, heads: int = 4, head
     }
 
 
-def block_params(rng: np.random.Generator) -> dict:
+def transition_params(rng: np.random.Generator, c_z: int = 128, expansion: int = 4, std: float = 0.02) -> dict:
+    w = lambda *shape: (rng.standard_normal(shape) * std).astype(np.float32)
+    hidden = expansion * c_z
     return {
+        "norm": {"scale": np.ones(c_z, np.float32), "bias": np.zeros(c_z, np.float32)},
+        "fc1": {"kernel": w(c_z, hidden)}, "fc2": {"kernel": w(c_z, hidden)}, "fc3": {"kernel": w(hidden, c_z)},
+    }
+
+
+def block_params(rng: np.random.Generator, transition: bool = False) -> dict:
+    """The four triangle sub-modules of a block; with ``transition`` also ``transition_z``."""
+    params = {
         "tri_mul_out": trimul_params(rng), "tri_mul_in": trimul_params(rng),
         "tri_att_start": triatt_params(rng), "tri_att_end": triatt_params(rng),
     }
+    if transition:
+        params["transition_z"] = transition_params(rng)
+    return params
 
 
 def pad_mask(n: int, n_pad: int) -> np.ndarray:

@@ -24,7 +24,8 @@ sys.path.insert(0, str(ROOT / "tests"))
 def main() -> int:
     from conftest import assert_parity
     from foldjax_b200 import _device as dev, _lib, cp
-    from foldjax_b200.synthetic import pad_mask, triatt_params, trimul_params
+    from foldjax_b200.block import triangle_block_forward
+    from foldjax_b200.synthetic import block_params, pad_mask, triatt_params, trimul_params
     from foldjax_b200.triangle import triangle_multiplication_forward
     from foldjax_b200.triangle_attention import triangle_attention_forward
 
@@ -37,6 +38,7 @@ def main() -> int:
     rng = np.random.default_rng(7)
     pm = dev.params_to_device(trimul_params(rng, std=0.05))
     pa = dev.params_to_device(triatt_params(rng, std=0.05))
+    pb = dev.params_to_device(block_params(np.random.default_rng(8), transition=True))
     gen = torch.Generator(device="cpu").manual_seed(11)
     z_full = torch.randn(n, n, 128, generator=gen).to(torch.bfloat16).cuda()
     mask_full = torch.from_numpy(pad_mask(n, max(1, n // 40))[0]).cuda()
@@ -62,7 +64,10 @@ def main() -> int:
              ("triatt starting", lambda: cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=True),
               lambda: triangle_attention_forward(pa, z_full, mask_full[None], starting=True)),
              ("triatt ending", lambda: cp.triangle_attention_cp(ctx, pa, z_tile, mask_full, starting=False),
-              lambda: triangle_attention_forward(pa, z_full, mask_full[None], starting=False))]
+              lambda: triangle_attention_forward(pa, z_full, mask_full[None], starting=False)),
+             # the whole pair track of a block, residual adds and the (row-local) pair transition included
+             ("block with transition", lambda: cp.triangle_block_cp(ctx, pb, z_tile, mask_full),
+              lambda: triangle_block_forward(pb, z_full[None], mask_full[None])[0])]
     for name, run_cp, run_single in cases:
         tile = run_cp()
         _lib.device_status()
@@ -72,7 +77,9 @@ def main() -> int:
             _lib.device_status()
             valid = mask_full.bool().any(dim=1)  # rows/cols with a valid key
             ok_rows = valid[:, None, None].expand_as(ref) if "ending" not in name else valid[None, :, None].expand_as(ref)
-            if "triatt" not in name:
+            if name.startswith("block"):  # fully padded rows and columns pass through both attention nodes
+                ok_rows = (valid[:, None, None] & valid[None, :, None]).expand_as(ref)
+            elif "triatt" not in name:
                 ok_rows = torch.ones_like(ref, dtype=torch.bool)
             try:
                 info = assert_parity(ref.float().cpu().numpy(), full.float().cpu().numpy(),
