@@ -174,7 +174,7 @@ def run_gpu(args) -> None:
     n = args.tokens
     rng = np.random.default_rng(3)
     params = dev.params_to_device(make_params(rng))
-    n_pad = n - int(round(n * 3012 / 3072)) if n >= 64 else 0
+    n_pad = args.pad_tokens if args.pad_tokens >= 0 else (n - int(round(n * 3012 / 3072)) if n >= 64 else 0)
     mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
     mask = mask_host.cuda()
     if world == 1:
@@ -338,6 +338,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=3072)
+    ap.add_argument("--pad-tokens", type=int, default=-1,
+                    help="trailing padded tokens in the mask (default: the 3012-of-3072 ratio of the headline config)")
     ap.add_argument("--cpu-tokens", type=int, default=320, help="size of the bounded CPU sample")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
