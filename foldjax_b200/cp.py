@@ -189,13 +189,18 @@ def triangle_multiplication_cp(
         msgs = trimul_incoming_msgs(grid)
         n_src, n_k = R, n_r
 
+    # Inside every n_c-row block the rows are grouped again in blocks of 64
+    # ([n_c/64][128][64][ld]): same bytes, so the messages do not change, but the
+    # projection's channel planes of one tile stay close together in memory.
+    rpb = 64 if n_c % 64 == 0 else n_c
     wp, wb = _ws("cp_proj", lib.b200tri_trimul_project_workspace_bytes())
     pa = _lib.TrimulProjectArgs(
         n_outer=n_outer, n_inner=n_inner, eps=float(eps), x=x.data_ptr(), xs_outer=xs_o, xs_inner=xs_i,
         mask=mptr, ms_outer=ms_o, ms_inner=ms_i,
         norm_in_scale=lv["norm_in.scale"].data_ptr(), norm_in_bias=lv["norm_in.bias"].data_ptr(),
         p_in=lv["p_in.kernel"].data_ptr(), g_in=lv["g_in.kernel"].data_ptr(),
-        a=a_loc.data_ptr(), b=b_loc.data_ptr(), ld=ld, chan_stride=n_c * ld, block_stride=blk, rows_per_block=n_c,
+        a=a_loc.data_ptr(), b=b_loc.data_ptr(), ld=ld, chan_stride=rpb * ld, block_stride=128 * rpb * ld,
+        rows_per_block=rpb,
         workspace=wp, workspace_bytes=wb)
     _call(lib.b200tri_trimul_project, pa)
 
@@ -213,6 +218,11 @@ def triangle_multiplication_cp(
 
     ldt = (n_c + 63) // 64 * 64
     t = _bf16_buf("cp_t", 128, n_r, ldt)
+    # t in the same blocked form ([n_r/64][128][64][ldt]) when the rows allow it;
+    # otherwise plain channel-major [128][n_r][ldt]
+    t_rpb = rpb if rpb == 64 else n_r
+    t_chan = t_rpb * ldt
+    t_row = 128 * ldt if rpb == 64 else ldt  # elements per output row of one launch's offset
     for s in range(m):
         if outgoing:
             a_ptr, a_src = a_all.data_ptr() + 2 * s * blk, m * blk
@@ -220,14 +230,17 @@ def triangle_multiplication_cp(
             a_ptr, a_src = a_all[s].data_ptr(), blk
         ca = _lib.TrimulContractArgs(
             n_i=n_c, n_j=n_c, n_k=n_k, n_src=n_src,
-            a=a_ptr, a_ld=ld, a_chan_stride=n_c * ld, a_src_stride=a_src,
-            b=b_all.data_ptr(), b_ld=ld, b_chan_stride=n_c * ld, b_src_stride=blk,
-            acc_in=None, out_f32=None, out_bf16=t.data_ptr() + 2 * s * n_c * ldt, out_ld=ldt,
-            out_chan_stride=n_r * ldt)
+            a=a_ptr, a_ld=ld, a_chan_stride=rpb * ld, a_src_stride=a_src,
+            b=b_all.data_ptr(), b_ld=ld, b_chan_stride=rpb * ld, b_src_stride=blk,
+            acc_in=None, out_f32=None, out_bf16=t.data_ptr() + 2 * s * n_c * t_row, out_ld=ldt,
+            out_chan_stride=t_chan,
+            a_rows_per_block=rpb, b_rows_per_block=rpb, out_rows_per_block=t_rpb,
+            a_block_stride=128 * rpb * ld, b_block_stride=128 * rpb * ld, out_block_stride=128 * t_rpb * ldt)
         _call(lib.b200tri_trimul_contract, ca)
     wp, wb = _ws("cp_fin", lib.b200tri_trimul_finish_workspace_bytes())
     fa = _lib.TrimulFinishArgs(
-        n_i=n_r, n_j=n_c, eps=float(eps), t=t.data_ptr(), t_ld=ldt, t_chan_stride=n_r * ldt,
+        n_i=n_r, n_j=n_c, eps=float(eps), t=t.data_ptr(), t_ld=ldt, t_chan_stride=t_chan,
+        t_rows_per_block=t_rpb, t_block_stride=128 * t_rpb * ldt,
         x=x.data_ptr(), xs_i=n_c * 128, xs_j=128,
         norm_in_scale=lv["norm_in.scale"].data_ptr(), norm_in_bias=lv["norm_in.bias"].data_ptr(),
         norm_out_scale=lv["norm_out.scale"].data_ptr(), norm_out_bias=lv["norm_out.bias"].data_ptr(),
