@@ -22,8 +22,12 @@
 // Persistent, one CTA per SM:
 //   warp 0        TMA producer (x tiles, weight chunks)
 //   warp 1        MMA issuer: D1[chunk] = xn . [W1c ; W2c]^T, then OUT += h . W3c^T
-//   warps 2-5     layer norm of the x tile in place; epilogue of OUT (+ residual)
-//   warps 6-13    activation: two threads per pair, 32 hidden units each per chunk
+//   warps 2-17    four worker warpgroups. Every chunk, each turns 16 of the 64 [a | b]
+//                 column pairs of its rows into hidden values (four threads per pair: the
+//                 activation is a dependent MUFU chain, so it wants many warps per
+//                 scheduler). The layer norm of tile t and the epilogue of its OUT
+//                 (+ residual) are extra duties of warpgroup t mod 4, slotted between
+//                 chunks of the neighbouring tiles.
 // Bound: the activation (two MUFU operations per hidden unit: 1024 per pair) and
 // the tensor pipe (393 kflop per pair) are within 25 % of each other; HBM moves
 // 2 x 256 B per pair (x doubles as the residual when the caller adds in place).
@@ -39,7 +43,8 @@ constexpr int HC = 64;  // hidden units per chunk
 constexpr int WSTAGES = 3;
 constexpr int XSTAGES = 2;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
-constexpr int THREADS = 14 * 32;
+constexpr int NWORK = 4;  // worker warpgroups
+constexpr int THREADS = 64 + NWORK * 128;
 
 struct Smem {
   uint8_t w12[WSTAGES][2 * SLAB_BYTES];  // rows 0-63: W1 chunk, 64-127: W2 chunk; [128][128 in] as two K slabs
@@ -97,11 +102,11 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm.d1_full[a], 1);
-      mbar_init(&sm.d1_empty[a], 8);
+      mbar_init(&sm.d1_empty[a], NWORK * 4);
       mbar_init(&sm.out_full[a], 1);
-      mbar_init(&sm.out_empty[a], 4);
+      mbar_init(&sm.out_empty[a], 4);  // the four warps of the warpgroup on epilogue duty
     }
-    mbar_init(&sm.h_full, 256);
+    mbar_init(&sm.h_full, NWORK * 128);
     mbar_init(&sm.h_empty, 1);
     fence_barrier_init();
   }
@@ -201,93 +206,138 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
         }
       }
     }
-  } else if (warp < 6) {
-    // ---- layer norm of tile `it`, then the output epilogue of tile `it - 1`
+  } else {
+    const int wg = (warp - 2) >> 2;
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
+    const int row = quarter * 32 + lane;  // pair inside the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    for (long long it = 0; it <= n_my; ++it) {
-      if (it < n_my) {
-        const int xs = static_cast<int>(it % XSTAGES);
-        if (!mbar_wait(&sm.x_full[xs], static_cast<uint32_t>((it / XSTAGES) & 1), p.status, ST_TIMEOUT_PROLOGUE)) break;
-        uint4 v[16];
-        ln_load_row(sm.x[xs], row, v);
-        ln_rows_inplace(v, sm.gamma2, sm.beta2, p.eps);
-        ln_store_row(sm.x[xs], row, v);
-        fence_proxy_async();
-        mbar_arrive(&sm.xn_full[xs]);
+    bool alive = true;
+
+    // Layer norm of one row in place, in three sweeps over shared memory (mean,
+    // variance, normalise) so that it needs few registers; same arithmetic and
+    // rounding points as ln_rows_inplace.
+    auto layer_norm_tile = [&](long long it) {
+      const int xs = static_cast<int>(it % XSTAGES);
+      if (!mbar_wait(&sm.x_full[xs], static_cast<uint32_t>((it / XSTAGES) & 1), p.status, ST_TIMEOUT_PROLOGUE)) {
+        alive = false;
+        return;
       }
-      if (it > 0) {
-        const long long jt = it - 1;
-        const uint32_t tb = static_cast<uint32_t>(jt & 1);
-        if (!mbar_wait(&sm.out_full[tb], static_cast<uint32_t>((jt >> 1) & 1), p.status, ST_TIMEOUT_EPILOGUE)) break;
-        tc_fence_after();
-        const long long r = (blockIdx.x + jt * static_cast<long long>(gridDim.x)) * 128 + row;
-        const long long off = r * 128;
+      uint8_t* tile = sm.x[xs];
+      float sum = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum += bf16_lo(w[e]) + bf16_hi(w[e]);
+      }
+      const float mean = sum * (1.0f / 128.0f);
+      float sq = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = bf16_lo(w[e]) - mean, b = bf16_hi(w[e]) - mean;
+          sq = fmaf(a, a, sq);
+          sq = fmaf(b, b, sq);
+        }
+      }
+      const float rstd = rsqrtf(sq * (1.0f / 128.0f) + p.eps);
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        uint4* ptr = reinterpret_cast<uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
+        const uint4 v = *ptr;
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = (bf16_lo(w[e]) - mean) * rstd, b = (bf16_hi(w[e]) - mean) * rstd;
+          w[e] = bf16x2_add(bf16x2_mul(pack_bf16x2(a, b), sm.gamma2[4 * c + e]), sm.beta2[4 * c + e]);
+        }
+        *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async();
+      mbar_arrive(&sm.xn_full[xs]);
+    };
+
+    auto epilogue_tile = [&](long long jt) {
+      const uint32_t tb = static_cast<uint32_t>(jt & 1);
+      if (!mbar_wait(&sm.out_full[tb], static_cast<uint32_t>((jt >> 1) & 1), p.status, ST_TIMEOUT_EPILOGUE)) {
+        alive = false;
+        return;
+      }
+      tc_fence_after();
+      const long long r = (blockIdx.x + jt * static_cast<long long>(gridDim.x)) * 128 + row;
+      const long long off = r * 128;
 #pragma unroll 1
-        for (int chunk = 0; chunk < 4; ++chunk) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + 256 + tb * 128 + chunk * 32, v);
-          tmem_ld_wait();
-          if (r < p.rows) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out + off + chunk * 32);
-            const uint4* res = p.residual ? reinterpret_cast<const uint4*>(p.residual + off + chunk * 32) : nullptr;
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + 256 + tb * 128 + chunk * 32, v);
+        tmem_ld_wait();
+        if (r < p.rows) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + off + chunk * 32);
+          const uint4* res = p.residual ? reinterpret_cast<const uint4*>(p.residual + off + chunk * 32) : nullptr;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t u[4];
+          for (int q = 0; q < 4; ++q) {
+            uint32_t u[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                u[e] = pack_bf16x2(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
-              if (res) {
-                const uint4 rv = res[q];
-                u[0] = bf16x2_add(rv.x, u[0]);
-                u[1] = bf16x2_add(rv.y, u[1]);
-                u[2] = bf16x2_add(rv.z, u[2]);
-                u[3] = bf16x2_add(rv.w, u[3]);
-              }
-              dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+            for (int e = 0; e < 4; ++e)
+              u[e] = pack_bf16x2(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
+            if (res) {
+              const uint4 rv = res[q];
+              u[0] = bf16x2_add(rv.x, u[0]);
+              u[1] = bf16x2_add(rv.y, u[1]);
+              u[2] = bf16x2_add(rv.z, u[2]);
+              u[3] = bf16x2_add(rv.w, u[3]);
             }
+            dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.out_empty[tb]);
-      }
-    }
-  } else {
-    // ---- activation: thread (half, row) turns 32 columns of a and of b into 32 hidden values
-    const int half = (warp - 6) >> 2;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    for (long long n = 0; n < total_n; ++n) {
-      const uint32_t d = static_cast<uint32_t>(n & 1);
-      if (!mbar_wait(&sm.d1_full[d], static_cast<uint32_t>((n >> 1) & 1), p.status, ST_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after();
-      uint32_t hv[16];
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {  // 16 columns of a and of b at a time
-        uint32_t a[16], b[16];
-        tmem_ld16(lane_addr + d * 128 + half * 32 + part * 16, a);
-        tmem_ld16(lane_addr + d * 128 + HC + half * 32 + part * 16, b);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          hv[8 * part + e] = swiglu_bf16x2(__uint_as_float(a[2 * e]), __uint_as_float(a[2 * e + 1]),
-                                           __uint_as_float(b[2 * e]), __uint_as_float(b[2 * e + 1]));
       }
       tc_fence_before();
       __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.out_empty[tb]);
+    };
+
+    // Where in a tile's chunk sequence the extra duties sit: the next tile's layer
+    // norm one chunk after the producer requested its x, the previous tile's
+    // epilogue at the second chunk (its last product was issued at the first).
+    const int x_at = nchunks > WSTAGES ? WSTAGES : nchunks - 1;
+    const int c_ln = x_at + 1 < nchunks ? x_at + 1 : nchunks - 1;
+    const int c_ep = nchunks > 1 ? 1 : 0;
+    if (wg == 0 && n_my > 0) layer_norm_tile(0);
+    for (long long n = 0; n < total_n && alive; ++n) {
+      const long long it = n / nchunks;
+      const int c = static_cast<int>(n % nchunks);
+      if (c == c_ln && it + 1 < n_my && ((it + 1) & (NWORK - 1)) == wg) layer_norm_tile(it + 1);
+      if (c == c_ep && it >= 1 && ((it - 1) & (NWORK - 1)) == wg) epilogue_tile(it - 1);
+      if (!alive) break;
+      // ---- activation: this thread's 16 columns of a and of b -> 16 hidden values
+      const uint32_t d = static_cast<uint32_t>(n & 1);
+      if (!mbar_wait(&sm.d1_full[d], static_cast<uint32_t>((n >> 1) & 1), p.status, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      uint32_t a[16], b[16], hv[8];
+      tmem_ld16(lane_addr + d * 128 + wg * 16, a);
+      tmem_ld16(lane_addr + d * 128 + HC + wg * 16, b);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
       if (lane == 0) mbar_arrive(&sm.d1_empty[d]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        hv[e] = swiglu_bf16x2(__uint_as_float(a[2 * e]), __uint_as_float(a[2 * e + 1]), __uint_as_float(b[2 * e]),
+                              __uint_as_float(b[2 * e + 1]));
       // the previous chunk's second product must have read h before it is overwritten
       if (!mbar_wait(&sm.h_empty, static_cast<uint32_t>((n & 1) ^ 1), p.status, ST_TIMEOUT_EPILOGUE)) break;
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        *reinterpret_cast<uint4*>(sm.h + sw128_offset(row, half * 4 + q)) =
+      for (int q = 0; q < 2; ++q)
+        *reinterpret_cast<uint4*>(sm.h + sw128_offset(row, wg * 2 + q)) =
             make_uint4(hv[4 * q], hv[4 * q + 1], hv[4 * q + 2], hv[4 * q + 3]);
       fence_proxy_async();
       mbar_arrive(&sm.h_full);
     }
+    if (alive && n_my > 0 && ((n_my - 1) & (NWORK - 1)) == wg) epilogue_tile(n_my - 1);
   }
 
   if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
