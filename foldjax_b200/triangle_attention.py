@@ -137,16 +137,21 @@ def attention_core(q, k, v, tri_bias, mask_bias, scale: float | None = None):
         v2[:, :, :n_k] = vf[bi].permute(0, 1, 3, 2).reshape(n_i, h * d, n_k).to(torch.float16)
         b2 = torch.zeros(h, n_j, ld, dtype=torch.bfloat16, device=v.device)
         b2[:, :, :n_k] = bf[bi, 0].to(torch.bfloat16)
-        # additive mask -> the multiplicative form the kernel takes, with inf = max |mask_bias|
+        # additive mask -> the multiplicative form the kernel takes, with inf = the largest
+        # finite |mask_bias|; -inf entries (the ring tests' spelling of a dropped key) become
+        # mask 0. A row with no valid key comes out as the uniform average over its keys,
+        # the model-level convention of the finite -1e9 mask (triangle_attention.py:138-142).
         mb = mf[bi, :, 0, 0, :].float().contiguous()
-        big = float(mb.abs().max().item()) if mb.numel() else 0.0
-        m01 = (1.0 + mb / big).contiguous() if big > 0 else torch.ones_like(mb)
+        finite = torch.isfinite(mb)
+        big = float(mb[finite].abs().max().item()) if bool(finite.any()) else 0.0
+        big = big if big > 0 else 1e9
+        m01 = torch.where(finite, 1.0 + mb / big, torch.zeros_like(mb)).contiguous()
         o2 = torch.empty(n_i, n_j, h * d, dtype=torch.bfloat16, device=v.device)
         args = _lib.TriattCoreArgs(
             n_i=n_i, n_j=n_j, n_k=n_k, heads=h, head_dim=d,
             q=q2.data_ptr(), k=k2.data_ptr(), vt=v2.data_ptr(), v_ld=ld,
             bias=b2.data_ptr(), bias_ld=ld, bias_head_stride=n_j * ld,
-            mask=m01.data_ptr(), ms_i=n_k, ms_k=1, inf=big if big > 0 else 1e9,
+            mask=m01.data_ptr(), ms_i=n_k, ms_k=1, inf=big,
             o=o2.data_ptr(), row_max=None, row_sum=None, unnormalized=0,
             workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
         )
