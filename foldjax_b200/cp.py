@@ -34,6 +34,7 @@ from .cp_plan import (
     Msg,
     grid_for,
     key_order,
+    padded_tokens,
     triatt_ending_msgs,
     triatt_starting_msgs,
     trimul_incoming_msgs,
@@ -77,6 +78,26 @@ def shard_pair(ctx: CPContext, z: torch.Tensor) -> torch.Tensor:
     n_r, n_c = ctx.grid.tile_shape(n)
     r, c = ctx.coords
     return z[r * n_r:(r + 1) * n_r, c * n_c:(c + 1) * n_c].contiguous()
+
+
+def pad_pair(grid: Grid, z: torch.Tensor, mask: torch.Tensor | None):
+    """Pad a full ``[N, N, C]`` pair tensor and its ``[N, N]`` mask to a token count
+    the grid tiles evenly: zero pairs, and mask 0 on the added rows and columns, so
+    the added tokens are dropped as keys and contribute nothing to the contraction
+    (the reference's padding, triangle.py:165-172, _cp_attention.py:265-279). The
+    caller crops the result back to ``[:N, :N]``. With mask None an all-ones mask of
+    the original size is made, because the padding must be masked."""
+    n = z.shape[0]
+    n_pad = padded_tokens(n, grid)
+    if mask is None:
+        mask = torch.ones(n, n, dtype=torch.float32, device=z.device)
+    if n_pad == n:
+        return z, mask
+    zp = torch.zeros((n_pad, n_pad) + tuple(z.shape[2:]), dtype=z.dtype, device=z.device)
+    zp[:n, :n] = z
+    mp = torch.zeros(n_pad, n_pad, dtype=mask.dtype, device=mask.device)
+    mp[:n, :n] = mask
+    return zp, mp
 
 
 # ------------------------------------------------------------------ exchange

@@ -59,6 +59,15 @@ class Grid:
         return n // self.rows, n // self.cols
 
 
+def padded_tokens(n: int, grid: Grid) -> int:
+    """Smallest token count >= n that the grid tiles evenly (a multiple of the
+    column count, which the row count divides). The reference pads the same way:
+    zero rows/columns in the pair tensor and dropped keys in the mask
+    (src/foldjax/models/boltz2/models/triangle/triangle.py:165-172,
+    src/foldjax/models/_cp_attention.py:265-279)."""
+    return (n + grid.cols - 1) // grid.cols * grid.cols
+
+
 def grid_for(cp_devices: int, layout: str | None = None) -> Grid:
     """cp_devices -> grid, mirroring the reference's option surface
     (``cp_devices`` / ``cp_layout``, src/foldjax/models/_cp.py:162-187) and

@@ -83,3 +83,42 @@ def test_message_lists_are_complete_and_local_copies_are_marked():
     for dst in grid.ranks():
         slots = sorted(m.slot for m in att if m.dst == dst and m.what == "kv")
         assert slots == [(c,) for c in range(grid.cols)]
+
+
+@pytest.mark.parametrize("rows,cols,n", [(2, 2, 13), (2, 4, 13), (3, 3, 13), (1, 2, 9)])
+def test_padding_to_the_grid_leaves_the_real_block_unchanged(rows, cols, n):
+    """Token counts the grid does not divide (the reference's Cannon test runs N = 12
+    and 13): zero-padded pairs and dropped padded keys give the unpadded result on
+    the real block, for the contraction and for the attention."""
+    from foldjax_b200.cp_plan import padded_tokens
+
+    grid = Grid(rows, cols)
+    n_pad = padded_tokens(n, grid)
+    assert n_pad % cols == 0 and n_pad % rows == 0 and 0 <= n_pad - n < cols
+    rng = np.random.default_rng(1000 + rows * 10 + cols)
+    a, b = rng.standard_normal((n, n, 3)), rng.standard_normal((n, n, 3))
+    ap, bp = np.zeros((n_pad, n_pad, 3)), np.zeros((n_pad, n_pad, 3))
+    ap[:n, :n], bp[:n, :n] = a, b
+    for direction in ("outgoing", "incoming"):
+        got = cpo.simulate_trimul(grid, ap, bp, direction)[:n, :n]
+        np.testing.assert_allclose(got, orc.triangle_contraction(a, b, direction), rtol=1e-12, atol=1e-12)
+    h, d = 2, 3
+    q, k, v = (rng.normal(size=(n, n, h, d), scale=0.5) for _ in range(3))
+    bias = rng.normal(size=(h, n, n), scale=4.0)
+    keep = rng.random((n, n)) > 0.25
+    keep[:, 0] = True
+    mb = np.where(keep, 0.0, -1e9)
+    ref = orc.attention_core(q.transpose(0, 2, 1, 3)[None], k.transpose(0, 2, 1, 3)[None], v.transpose(0, 2, 1, 3)[None],
+                             bias[None, None], mb[None, :, None, None, :])[0].transpose(0, 2, 1, 3)
+
+    def pad(x, axes, fill=0.0):
+        shape = list(x.shape)
+        for ax in axes:
+            shape[ax] = n_pad
+        out = np.full(shape, fill)
+        out[tuple(slice(0, s) for s in x.shape)] = x
+        return out
+
+    qp, kp, vp = pad(q, (0, 1)), pad(k, (0, 1)), pad(v, (0, 1))
+    got = cpo.simulate_triatt(grid, qp, kp, vp, pad(bias, (1, 2)), pad(mb, (0, 1), fill=-np.inf), True)[:n, :n]
+    np.testing.assert_allclose(got, ref, rtol=1e-9, atol=1e-9)
