@@ -173,14 +173,22 @@ def run_gpu(args) -> None:
 
     n = args.tokens
     rng = np.random.default_rng(3)
-    params = dev.params_to_device(make_params(rng))
+    from foldjax_b200.synthetic import block_params
+
+    # one parameter set per block of the trunk slice (--blocks, default 1 = the headline block)
+    trunk = [dev.params_to_device(make_params(rng) if not args.transition else block_params(rng, transition=True))
+             for _ in range(args.blocks)]
+    params = trunk[0]
     n_pad = args.pad_tokens if args.pad_tokens >= 0 else (n - int(round(n * 3012 / 3072)) if n >= 64 else 0)
     mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
     mask = mask_host.cuda()
     if world == 1:
         gen = torch.Generator(device="cuda").manual_seed(3)
         z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
-        run_block = lambda zz, mm: triangle_block_forward(params, zz, mm)
+        def run_block(zz, mm):
+            for blk in trunk:
+                zz = triangle_block_forward(blk, zz, mm)
+            return zz
         grid_name = "single GPU"
     else:
         # one complex sharded over an R x C grid: every rank owns one tile of z (2-D
@@ -193,7 +201,10 @@ def run_gpu(args) -> None:
         z = torch.randn(n_r, n_c, 128, device="cuda", generator=gen).to(torch.bfloat16)
         mask = mask[0].contiguous()
         mask_host = mask_host[0]
-        run_block = lambda zz, mm: cp.triangle_block_cp(ctx, params, zz, mm)
+        def run_block(zz, mm):
+            for blk in trunk:
+                zz = cp.triangle_block_cp(ctx, blk, zz, mm)
+            return zz
         grid_name = f"2-D context parallel {ctx.grid.rows}x{ctx.grid.cols}, NCCL point-to-point tile exchange"
     z_host = torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True)
     z_host.copy_(z)
@@ -279,12 +290,12 @@ def run_gpu(args) -> None:
         return
 
     ms_step = ms_total / args.steps
-    flops = block_flops(n)
+    flops = args.blocks * (block_flops(n) + (2.0 * n * n * 3 * 128 * 512 if args.transition else 0.0))
     peaks, peak_kind = measured_peaks()
     core_ms, core_n = ktimes["triatt_core"]
     core_avg = core_ms / max(core_n, 1)
     # QK^T + PV of the two attention ops of a step, this rank's share (one launch per key tile)
-    core_flops_rank = 2.0 * 4.0 * n**3 * 128.0 / world * args.steps
+    core_flops_rank = 2.0 * 4.0 * n**3 * 128.0 / world * args.steps * args.blocks
     achieved = core_flops_rank / (core_ms * 1e-3) / 1e12 if core_ms else None
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
     shares = {k: round(v[0] / max(sum(t[0] for t in ktimes.values()), 1e-9), 4) for k, v in ktimes.items()}
@@ -298,7 +309,8 @@ def run_gpu(args) -> None:
         "config": {
             "workload": f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
                         "tri-mult out+in, tri-attn start+end, residual adds fused",
-            "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops,
+            "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops, "blocks_per_step": args.blocks,
+            "pair_transition_in_step": bool(args.transition),
             "parallelism": grid_name,
             "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
         },
@@ -338,6 +350,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=3072)
+    ap.add_argument("--blocks", type=int, default=1,
+                    help="blocks per step, each with its own weights (48 = the trunk of the headline config)")
+    ap.add_argument("--transition", action="store_true",
+                    help="include the pair transition in every block of the step (and in its flop count)")
     ap.add_argument("--pad-tokens", type=int, default=-1,
                     help="trailing padded tokens in the mask (default: the 3012-of-3072 ratio of the headline config)")
     ap.add_argument("--cpu-tokens", type=int, default=320, help="size of the bounded CPU sample")
