@@ -211,7 +211,7 @@ def run_gpu(args) -> None:
     out_host = torch.empty_like(z_host).pin_memory()
 
     def run_e2e():
-        if world == 1:
+        if world == 1 and args.blocks == 1:
             return triangle_block_forward(params, z_host, mask_host, out=out_host)
         zd = z_host.cuda(non_blocking=True)
         md = mask_host.cuda(non_blocking=True)
