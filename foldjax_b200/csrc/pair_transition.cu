@@ -22,12 +22,12 @@
 // Persistent, one CTA per SM:
 //   warp 0        TMA producer (x tiles, weight chunks)
 //   warp 1        MMA issuer: D1[chunk] = xn . [W1c ; W2c]^T, then OUT += h . W3c^T
-//   warps 2-17    four worker warpgroups. Every chunk, each turns 16 of the 64 [a | b]
-//                 column pairs of its rows into hidden values (four threads per pair: the
-//                 activation is a dependent MUFU chain, so it wants many warps per
-//                 scheduler). The layer norm of tile t and the epilogue of its OUT
-//                 (+ residual) are extra duties of warpgroup t mod 4, slotted between
-//                 chunks of the neighbouring tiles.
+//   warps 2-5     layer norm of the x tile in place (three register-light sweeps over
+//                 shared memory); epilogue of OUT (+ residual)
+//   warps 6-21    activation: four warpgroups, each turns 16 of the 64 [a | b] column
+//                 pairs of every row into hidden values per chunk (four threads per
+//                 pair). All of them must have stored their part before the second
+//                 product of the chunk can start, so these warps carry no other duty.
 // Bound: the activation (two MUFU operations per hidden unit: 1024 per pair) and
 // the tensor pipe (393 kflop per pair) are within 25 % of each other; HBM moves
 // 2 x 256 B per pair (x doubles as the residual when the caller adds in place).
@@ -43,8 +43,8 @@ constexpr int HC = 64;  // hidden units per chunk
 constexpr int WSTAGES = 3;
 constexpr int XSTAGES = 2;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
-constexpr int NWORK = 4;  // worker warpgroups
-constexpr int THREADS = 64 + NWORK * 128;
+constexpr int NWORK = 4;  // activation warpgroups
+constexpr int THREADS = 64 + 128 + NWORK * 128;
 
 struct Smem {
   uint8_t w12[WSTAGES][2 * SLAB_BYTES];  // rows 0-63: W1 chunk, 64-127: W2 chunk; [128][128 in] as two K slabs
@@ -207,7 +207,8 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       }
     }
   } else {
-    const int wg = (warp - 2) >> 2;
+    const bool act = warp >= 6;
+    const int wg = act ? (warp - 6) >> 2 : 0;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // pair inside the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -300,19 +301,14 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       if (lane == 0) mbar_arrive(&sm.out_empty[tb]);
     };
 
-    // Where in a tile's chunk sequence the extra duties sit: the next tile's layer
-    // norm one chunk after the producer requested its x, the previous tile's
-    // epilogue at the second chunk (its last product was issued at the first).
-    const int x_at = nchunks > WSTAGES ? WSTAGES : nchunks - 1;
-    const int c_ln = x_at + 1 < nchunks ? x_at + 1 : nchunks - 1;
-    const int c_ep = nchunks > 1 ? 1 : 0;
-    if (wg == 0 && n_my > 0) layer_norm_tile(0);
-    for (long long n = 0; n < total_n && alive; ++n) {
-      const long long it = n / nchunks;
-      const int c = static_cast<int>(n % nchunks);
-      if (c == c_ln && it + 1 < n_my && ((it + 1) & (NWORK - 1)) == wg) layer_norm_tile(it + 1);
-      if (c == c_ep && it >= 1 && ((it - 1) & (NWORK - 1)) == wg) epilogue_tile(it - 1);
-      if (!alive) break;
+    if (!act) {
+      // ---- layer norm of tile `it`, then the output epilogue of tile `it - 1`
+      for (long long it = 0; it <= n_my && alive; ++it) {
+        if (it < n_my) layer_norm_tile(it);
+        if (it > 0 && alive) epilogue_tile(it - 1);
+      }
+    }
+    for (long long n = 0; act && n < total_n; ++n) {
       // ---- activation: this thread's 16 columns of a and of b -> 16 hidden values
       const uint32_t d = static_cast<uint32_t>(n & 1);
       if (!mbar_wait(&sm.d1_full[d], static_cast<uint32_t>((n >> 1) & 1), p.status, ST_TIMEOUT_EPILOGUE)) break;
@@ -337,7 +333,6 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       fence_proxy_async();
       mbar_arrive(&sm.h_full);
     }
-    if (alive && n_my > 0 && ((n_my - 1) & (NWORK - 1)) == wg) epilogue_tile(n_my - 1);
   }
 
   if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
