@@ -72,8 +72,8 @@ struct Params {
 // fp32 accumulators and are rounded to bf16 first, like the reference's matmul output.
 __device__ __forceinline__ uint32_t swiglu_bf16x2(float a0, float a1, float b0, float b1) {
   const uint32_t a = pack_bf16x2(a0, a1);
-  const uint32_t s = pack_bf16x2(sigmoid_f32(bf16_lo(a)), sigmoid_f32(bf16_hi(a)));
-  return bf16x2_mul(bf16x2_mul(a, s), pack_bf16x2(b0, b1));
+  const float2 s = sigmoid_f32x2(make_float2(bf16_lo(a), bf16_hi(a)));
+  return bf16x2_mul(bf16x2_mul(a, pack_bf16x2(s.x, s.y)), pack_bf16x2(b0, b1));
 }
 
 __global__ void __launch_bounds__(THREADS, 1)

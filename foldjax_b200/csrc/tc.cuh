@@ -288,16 +288,35 @@ __device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// sigmoid in fp32 to ~1e-6 relative (ex2 + rcp). The gates are rounded to bf16
+// sigmoid in fp32 to ~1e-6 relative: one ex2 and one rcp (the flushing approximate
+// forms, a single MUFU operation each with no range fix-up around them), the
+// multiply and the add packed two at a time. The gates are rounded to bf16
 // afterwards like the reference's; a cheaper tanh-based sigmoid (2^-11) flips
 // that rounding often enough to push the mean error past the parity budget.
-__device__ __forceinline__ float sigmoid_f32(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+// Saturation is exact: x -> -inf gives rcp(inf) = 0, x -> +inf gives rcp(1) = 1.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_f32(float x) { return fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * x)); }
+__device__ __forceinline__ float2 sigmoid_f32x2(float2 x) {
+  const float2 t = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  const float2 d = __fadd2_rn(make_float2(fast_exp2(t.x), fast_exp2(t.y)), make_float2(1.0f, 1.0f));
+  return make_float2(fast_rcp(d.x), fast_rcp(d.y));
+}
 
 // bf16(sigmoid(bf16(g0))), bf16(sigmoid(bf16(g1))) packed: the reference's
 // sigmoid(x @ w) on a bf16 trunk.
 __device__ __forceinline__ uint32_t sigmoid_bf16x2(float g0, float g1) {
   const uint32_t g = pack_bf16x2(g0, g1);
-  return pack_bf16x2(sigmoid_f32(bf16_lo(g)), sigmoid_f32(bf16_hi(g)));
+  const float2 s = sigmoid_f32x2(make_float2(bf16_lo(g), bf16_hi(g)));
+  return pack_bf16x2(s.x, s.y);
 }
 // max of three (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -305,12 +324,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 // Byte offset of (row, 16-byte chunk) inside a K-major tile with 128-byte rows
 // under the 128-byte swizzle (the layout TMA writes and tcgen05.mma reads).
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
