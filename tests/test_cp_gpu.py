@@ -27,6 +27,6 @@ def _run(world: int, tokens: int) -> str:
     return done.stdout
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 512), (4, 512), (8, 1024)])
+@pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (4, 512), (8, 1024)])
 def test_context_parallel_matches_single_gpu(world, tokens):
     print(_run(world, tokens))
