@@ -13,6 +13,7 @@ It restates, in plain NumPy, the arithmetic of the reference's XLA (jnp) path
 * triangle multiplication  src/foldjax/models/boltz2/models/triangle/triangle.py:78-129, 227-241
 * triangle attention ... src/foldjax/models/boltz2/models/triangle/triangle_attention.py:125-162, 346-455
 * pair transition ...... src/foldjax/models/boltz2/models/primitives/transition.py:99-112
+* attention with pair bias  src/foldjax/models/boltz2/models/primitives/attention.py:19-140
 
 The arithmetic itself lives in a dependency that is not vendored in the
 reference: jax / jaxlib 0.10.1 (uv.lock), i.e. XLA's dot, softmax, sigmoid and
@@ -26,7 +27,9 @@ tests/models/boltz2/test_triangle_attention_checkpoint_parity.py:94-147).
 checkout and runs them on seeded inputs; the outputs are committed as
 ``tests/golden/*.npz`` and ``tests/test_oracle.py`` holds this oracle to them.
 The transition is pinned the same way by the ``TorchTransition`` module of
-tests/models/boltz2/test_transition_forward.py:11-33 (1e-5).
+tests/models/boltz2/test_transition_forward.py:11-33 (1e-5), the single-track attention
+by ``_torch_attention_pair_bias_forward`` of
+tests/models/boltz2/test_attention_checkpoint_parity.py:109-148 (2e-4).
 
 Two precisions are offered by every function:
 
@@ -281,6 +284,57 @@ def random_transition_params(rng: np.random.Generator, c_z: int = 128, expansion
         "fc1": {"kernel": w(c_z, hidden)},
         "fc2": {"kernel": w(c_z, hidden)},
         "fc3": {"kernel": w(hidden, c_z)},
+    }
+
+
+# ------------------------------------------------ single attention with pair bias
+def attention_pair_bias(params: Params, s: np.ndarray, z: np.ndarray, mask: np.ndarray, k_in: np.ndarray | None = None,
+                        inf: float = 1e6, eps: float = 1e-5, dtype: str = "float64") -> np.ndarray:
+    """attention.py:19-140 (XLA path), as the Pairformer block calls it
+    (trunk_blocks/pairformer.py:188-203): s [B,N,c_s] (already layer-normed by the
+    caller) and z [B,N,N,c_z] arrive in float32 whatever the trunk dtype, so there is
+    no bf16 mode: ``dtype`` is "float64" or "float32". mask [B,N] -> [B,N,c_s]."""
+    if dtype not in ("float64", "float32"):
+        raise ValueError("the single-track attention runs in float32 in the reference; use float64 or float32")
+    work = np.float64 if dtype == "float64" else np.float32
+    f = lambda name, leaf="kernel": np.asarray(params[name][leaf], dtype=work)
+    s = np.asarray(s, dtype=work)
+    k_in = s if k_in is None else np.asarray(k_in, dtype=work)
+    batch, n, c_s = s.shape
+    heads = f("proj_z").shape[-1]
+    hd = c_s // heads
+    q = (s @ f("proj_q") + f("proj_q", "bias")).reshape(batch, n, heads, hd)  # :46-52
+    g = _sigmoid(s @ f("proj_g"))  # :53
+    k = (k_in @ f("proj_k")).reshape(batch, -1, heads, hd)  # :54-62
+    v = (k_in @ f("proj_v")).reshape(batch, -1, heads, hd)
+    zf = np.asarray(z, dtype=work)
+    mean = zf.mean(-1, keepdims=True)
+    var = np.square(zf - mean).mean(-1, keepdims=True)
+    zn = (zf - mean) / np.sqrt(var + work(eps)) * f("proj_z_norm", "scale") + f("proj_z_norm", "bias")  # :64-69
+    bias = np.transpose(zn @ f("proj_z"), (0, 3, 1, 2))  # [B,H,N,N]  :70-71
+    mask_bias = (1.0 - np.asarray(mask, dtype=work))[:, None, None, :] * work(-inf)  # :92
+    attn = np.einsum("bihd,bjhd->bhij", q, k) / np.sqrt(work(hd)) + bias + mask_bias  # :134-136
+    attn = attn - attn.max(-1, keepdims=True)
+    attn = np.exp(attn)
+    attn = attn / attn.sum(-1, keepdims=True)
+    out = np.einsum("bhij,bjhd->bihd", attn, v).reshape(batch, n, c_s)
+    return (g * out) @ f("proj_o")  # :116-117
+
+
+def random_attention_pair_bias_params(rng: np.random.Generator, c_s: int = 384, c_z: int = 128, heads: int = 16,
+                                      std: float = 0.02, ln_noise: float = 0.0) -> dict:
+    def w(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    return {
+        "proj_q": {"kernel": w(c_s, c_s), "bias": w(c_s)},
+        "proj_k": {"kernel": w(c_s, c_s)},
+        "proj_v": {"kernel": w(c_s, c_s)},
+        "proj_g": {"kernel": w(c_s, c_s)},
+        "proj_z_norm": {"scale": (1.0 + ln_noise * rng.standard_normal(c_z)).astype(np.float32),
+                        "bias": (ln_noise * rng.standard_normal(c_z)).astype(np.float32)},
+        "proj_z": {"kernel": w(c_z, heads)},
+        "proj_o": {"kernel": w(c_s, c_s)},
     }
 
 

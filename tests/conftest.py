@@ -67,6 +67,21 @@ def load_transition_golden(name: str):
     return params, g["x"], {"whole": g["out"], "chunked": g["out.chunked"]}
 
 
+def load_attention_pair_bias_golden(name: str):
+    """Golden case -> (params in the reference's [in,out] layout, s, k_in, z, mask, output)."""
+    g = np.load(GOLDEN / name)
+    params = {
+        "proj_q": {"kernel": _t(g["w.proj_q.weight"]), "bias": g["w.proj_q.bias"]},
+        "proj_k": {"kernel": _t(g["w.proj_k.weight"])},
+        "proj_v": {"kernel": _t(g["w.proj_v.weight"])},
+        "proj_g": {"kernel": _t(g["w.proj_g.weight"])},
+        "proj_z_norm": {"scale": g["w.proj_z.0.weight"], "bias": g["w.proj_z.0.bias"]},
+        "proj_z": {"kernel": _t(g["w.proj_z.1.weight"])},
+        "proj_o": {"kernel": _t(g["w.proj_o.weight"])},
+    }
+    return params, g["s"], g["k_in"], g["z"], g["mask"], g["out"]
+
+
 @pytest.fixture(scope="session")
 def cuda_device():
     torch = pytest.importorskip("torch")

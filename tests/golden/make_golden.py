@@ -17,6 +17,8 @@ equal to its jnp path within 2e-4 / 3e-4:
 and a PyTorch module for the pair transition, asserted equal to 1e-5:
 
 * tests/models/boltz2/test_transition_forward.py ``TorchTransition`` (lines 11-33)
+* tests/models/boltz2/test_attention_checkpoint_parity.py
+    ``_torch_attention_pair_bias_forward`` (lines 109-148, asserted to 2e-4)
 
 This script imports those test modules from the checkout *unmodified* (JAX
 and the FoldJAX package, which the modules import at the top but the helpers do
@@ -59,7 +61,9 @@ def _load_reference_test(rel: str):
     sys.modules["jax"].numpy = sys.modules["jax.numpy"]
     _stub("foldjax.models.boltz2.bridge.torch_mapping", map_triangle_multiplication_state_dict=None,
           map_triangle_attention_state_dict=None, map_transition_state_dict=None)
+    sys.modules["foldjax.models.boltz2.bridge.torch_mapping"].map_attention_pair_bias_state_dict = None
     _stub("foldjax.models.boltz2.models.primitives")
+    _stub("foldjax.models.boltz2.models.primitives.attention", attention_pair_bias_forward=None)
     _stub("foldjax.models.boltz2.models.primitives.transition", transition_forward=None)
     _stub("foldjax.models.boltz2.models.triangle.triangle", triangle_multiplication_forward=None)
     _stub("foldjax.models.boltz2.models.triangle.triangle_attention", triangle_attention_forward=None)
@@ -148,6 +152,28 @@ def make_transition(mod, seed: int, rows: tuple[int, ...], dim: int, hidden: int
     return out
 
 
+def make_attention_pair_bias(mod, seed: int, n: int, c_s: int, c_z: int, heads: int) -> dict:
+    gen = torch.Generator().manual_seed(seed)
+    prefix = mod.PREFIX
+    state = {
+        f"{prefix}.proj_q.weight": _w(gen, c_s, c_s), f"{prefix}.proj_q.bias": _w(gen, c_s),
+        f"{prefix}.proj_k.weight": _w(gen, c_s, c_s), f"{prefix}.proj_v.weight": _w(gen, c_s, c_s),
+        f"{prefix}.proj_g.weight": _w(gen, c_s, c_s), f"{prefix}.proj_o.weight": _w(gen, c_s, c_s),
+        f"{prefix}.proj_z.0.weight": 1.0 + _w(gen, c_z), f"{prefix}.proj_z.0.bias": _w(gen, c_z),
+        f"{prefix}.proj_z.1.weight": _w(gen, heads, c_z, std=0.5),
+    }
+    s = torch.randn(1, n, c_s, generator=gen)
+    k_in = torch.randn(1, n, c_s, generator=gen)
+    z = torch.randn(1, n, n, c_z, generator=gen)
+    mask = (torch.rand(1, n, generator=gen) < 0.8).float()
+    mask[0, 0] = 1.0
+    out = {"s": s.numpy(), "k_in": k_in.numpy(), "z": z.numpy(), "mask": mask.numpy()}
+    for key, val in state.items():
+        out["w." + key[len(prefix) + 1:]] = val.numpy()
+    out["out"] = mod._torch_attention_pair_bias_forward(state, s, z, mask, k_in).detach().numpy()
+    return out
+
+
 def main() -> None:
     torch.manual_seed(0)
     tm = _load_reference_test("tests/models/boltz2/test_triangle_checkpoint_parity.py")
@@ -161,6 +187,10 @@ def main() -> None:
     tr = _load_reference_test("tests/models/boltz2/test_transition_forward.py")
     np.savez_compressed(OUT / "transition_d5_h11.npz", **make_transition(tr, 15, rows=(2, 3), dim=5, hidden=11))
     np.savez_compressed(OUT / "transition_d128_h512.npz", **make_transition(tr, 16, rows=(3, 8), dim=128, hidden=512))
+    ap = _load_reference_test("tests/models/boltz2/test_attention_checkpoint_parity.py")
+    np.savez_compressed(OUT / "attention_pair_bias_n7.npz", **make_attention_pair_bias(ap, 17, n=7, c_s=12, c_z=8, heads=3))
+    np.savez_compressed(OUT / "attention_pair_bias_n12_c96.npz",  # head dim 24 and c_z 128 as in the trunk
+                        **make_attention_pair_bias(ap, 18, n=12, c_s=96, c_z=128, heads=4))
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 
