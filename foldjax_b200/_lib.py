@@ -138,6 +138,18 @@ class PairTransitionArgs(C.Structure):
     ]
 
 
+class AttentionPairBiasArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("c_s", C.c_int32), ("c_z", C.c_int32), ("heads", C.c_int32),
+        ("eps", C.c_float), ("inf", C.c_float),
+        ("s", C.c_void_p), ("k_in", C.c_void_p), ("z", C.c_void_p), ("mask", C.c_void_p),
+        ("proj_q", C.c_void_p), ("proj_q_bias", C.c_void_p), ("proj_k", C.c_void_p), ("proj_v", C.c_void_p),
+        ("proj_g", C.c_void_p), ("proj_z_norm_scale", C.c_void_p), ("proj_z_norm_bias", C.c_void_p),
+        ("proj_z", C.c_void_p), ("proj_o", C.c_void_p),
+        ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 # C struct name -> ctypes mirror (tests compare sizeof on both sides)
 STRUCTS = {
     "b200tri_trimul_args": TrimulArgs,
@@ -149,6 +161,7 @@ STRUCTS = {
     "b200tri_triatt_core_args": TriattCoreArgs,
     "b200tri_triatt_finish_args": TriattFinishArgs,
     "b200tri_pair_transition_args": PairTransitionArgs,
+    "b200tri_attention_pair_bias_args": AttentionPairBiasArgs,
 }
 
 # name -> (restype, argtypes); every symbol include/b200tri.h declares.
@@ -179,6 +192,8 @@ SIGNATURES = {
     "b200tri_triatt_finish": (C.c_int, [C.POINTER(TriattFinishArgs), C.c_void_p]),
     "b200tri_pair_transition_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_pair_transition": (C.c_int, [C.POINTER(PairTransitionArgs), C.c_void_p]),
+    "b200tri_attention_pair_bias_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "b200tri_attention_pair_bias": (C.c_int, [C.POINTER(AttentionPairBiasArgs), C.c_void_p]),
 }
 
 _lib = None
@@ -219,7 +234,7 @@ def device_status() -> int:
 
 
 KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish",
-           "pair_transition")
+           "pair_transition", "pair_bias")
 
 
 def kernel_times() -> dict[str, tuple[float, int]]:

@@ -49,7 +49,7 @@ int b200tri_device_status(void);
  *   kernels with CUDA events on the launching stream. b200tri_timing_read
  *   synchronises the device and returns, for a kernel name ("trimul_project",
  *   "trimul_contract", "trimul_finish", "triatt_project", "triatt_core",
- *   "triatt_finish", "pair_transition"), the summed duration in ms and the number of launches since
+ *   "triatt_finish", "pair_transition", "pair_bias"), the summed duration in ms and the number of launches since
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
 /* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
@@ -370,6 +370,47 @@ typedef struct {
 
 size_t b200tri_pair_transition_workspace_bytes(int32_t hidden);
 int b200tri_pair_transition(const b200tri_pair_transition_args* args, b200tri_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Single-representation attention with pair bias (the other reader of z in a
+ * Pairformer block).
+ * Replaces: attention_pair_bias_forward,
+ *   src/foldjax/models/boltz2/models/primitives/attention.py:19-140, as called by
+ *   src/foldjax/models/boltz2/models/trunk_blocks/pairformer.py:188-203 with s and z
+ *   promoted to float32.
+ * Computes  out = (sigmoid(s @ proj_g) * softmax_j(q_h . k_h / sqrt(d) + bias_h[i,j]
+ *                  + (1 - mask_j) * -inf) v_h) @ proj_o
+ * with q = s @ proj_q + proj_q_bias, k/v = k_in @ proj_k/proj_v and
+ * bias = LN(z) @ proj_z. s, k_in, mask and out are fp32 (as in the reference); z and
+ * all parameters are bf16 (the trunk dtype) and are promoted to fp32. Returns the
+ * update (the caller adds the residual). `multiplicity` is 1. */
+typedef struct {
+  int32_t n;        /* tokens */
+  int32_t c_s;      /* heads * 24 (384 in the Pairformer) */
+  int32_t c_z;      /* 128 */
+  int32_t heads;    /* <= 16 */
+  float eps;        /* layer norm of z */
+  float inf;        /* mask constant (1e6 in the reference) */
+  const void* s;    /* fp32 [n][c_s], the caller's layer-normed single representation */
+  const void* k_in; /* fp32 [n][c_s] or NULL (= s) */
+  const void* z;    /* bf16 [n][n][128] */
+  const void* mask; /* fp32 [n], 1 = valid token */
+  const void* proj_q;      /* bf16 [c_s][c_s]  ([in, out]) */
+  const void* proj_q_bias; /* bf16 [c_s] */
+  const void* proj_k;
+  const void* proj_v;
+  const void* proj_g;
+  const void* proj_z_norm_scale; /* bf16 [128] */
+  const void* proj_z_norm_bias;
+  const void* proj_z;      /* bf16 [128][heads] */
+  const void* proj_o;      /* bf16 [c_s][c_s] */
+  void* out;        /* fp32 [n][c_s] */
+  void* workspace;
+  size_t workspace_bytes;
+} b200tri_attention_pair_bias_args;
+
+size_t b200tri_attention_pair_bias_workspace_bytes(int32_t n, int32_t c_s, int32_t heads);
+int b200tri_attention_pair_bias(const b200tri_attention_pair_bias_args* args, b200tri_stream_t stream);
 
 #ifdef __cplusplus
 }
