@@ -84,6 +84,8 @@ def select_by_env(model_op: str, value: str = BACKEND, environ=os.environ) -> st
 
 def operators() -> dict[str, Callable]:
     """The operator entry points this backend provides, by the reference's names."""
+    from .attention import attention_pair_bias_forward
+    from .transition import transition_forward
     from .triangle import triangle_multiplication_forward
     from .triangle_attention import attention_core, triangle_attention_forward
 
@@ -91,4 +93,6 @@ def operators() -> dict[str, Callable]:
         "triangle_multiplication_forward": triangle_multiplication_forward,
         "triangle_attention_forward": triangle_attention_forward,
         "attention_core": attention_core,
+        "transition_forward": transition_forward,
+        "attention_pair_bias_forward": attention_pair_bias_forward,
     }

@@ -58,4 +58,5 @@ def test_env_selection_uses_the_reference_variable_names():
 
 def test_operator_names_match_the_reference():
     ops = backend.operators()
-    assert set(ops) == {"triangle_multiplication_forward", "triangle_attention_forward", "attention_core"}
+    assert set(ops) == {"triangle_multiplication_forward", "triangle_attention_forward", "attention_core",
+                        "transition_forward", "attention_pair_bias_forward"}
