@@ -21,6 +21,7 @@ fp32), which is what the reference's ring does with its two passes
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Any, Mapping
 
@@ -42,7 +43,8 @@ from .cp_plan import (
 )
 from .triangle import _leaf
 
-COMM_SMS = 8  # SMs left to NCCL's send/recv kernels while a tile exchange is in flight
+# SMs left to NCCL's send/recv kernels while a tile exchange is in flight (B200TRI_COMM_SMS overrides)
+COMM_SMS = int(os.environ.get("B200TRI_COMM_SMS", "8"))
 
 
 @dataclass
