@@ -1,7 +1,7 @@
 """Generate the golden vectors that pin the oracle.
 
 Run in a container that has the reference checkout (eightmm/FoldJAX) at
-``$FOLDJAX_REFERENCE`` (default ``/root/reference``) and PyTorch:
+``$FOLDJAX_REFERENCE`` (default: a ``reference`` directory beside this repository) and PyTorch:
 
     python tests/golden/make_golden.py
 
@@ -40,7 +40,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("FOLDJAX_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("FOLDJAX_REFERENCE", Path(__file__).resolve().parents[3] / "reference"))
 OUT = Path(__file__).resolve().parent
 
 
