@@ -356,7 +356,7 @@ def main() -> None:
                     help="include the pair transition in every block of the step (and in its flop count)")
     ap.add_argument("--pad-tokens", type=int, default=-1,
                     help="trailing padded tokens in the mask (default: the 3012-of-3072 ratio of the headline config)")
-    ap.add_argument("--cpu-tokens", type=int, default=320, help="size of the bounded CPU sample")
+    ap.add_argument("--cpu-tokens", type=int, default=384, help="size of the bounded CPU sample")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
