@@ -214,6 +214,7 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int row = quarter * 32 + lane;  // TMEM lane: a pair for q/k/bias, a channel for vT
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t qs = pack_bf16x2(p.q_scale, p.q_scale);
+    const float q_inv = 1.0f / bf16_lo(qs);
     uint32_t it = 0;
     for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
       const int o = static_cast<int>(tile / p.tiles_inner);
@@ -237,8 +238,13 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               uint32_t v2 = pack_bf16x2(__uint_as_float(r[8 * g4 + 2 * e]), __uint_as_float(r[8 * g4 + 2 * e + 1]));
-              if (chunk < 4)  // q / sqrt(d): the quotient of two bf16 numbers, rounded to bf16
-                v2 = pack_bf16x2(__fdiv_rn(bf16_lo(v2), bf16_lo(qs)), __fdiv_rn(bf16_hi(v2), bf16_lo(qs)));
+              // q / sqrt(d): the quotient of two bf16 numbers, rounded to bf16. The divisor
+              // is bf16(sqrt(32)) = 181/32 and q has an 8-bit significand, so the exact
+              // quotient is a multiple of 1/181 of its ulp scale and never closer than
+              // ~1e-5 (relative) to a bf16 rounding boundary: any fp32 value within 1e-6 of
+              // it, such as the product with the rounded reciprocal, rounds to the same bf16
+              // as the true division.
+              if (chunk < 4) v2 = pack_bf16x2(bf16_lo(v2) * q_inv, bf16_hi(v2) * q_inv);
               u[e] = v2;
             }
             dst[g4] = make_uint4(u[0], u[1], u[2], u[3]);

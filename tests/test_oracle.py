@@ -100,3 +100,19 @@ def test_layer_norm_rounds_before_affine_in_bf16():
     assert np.array_equal(y, orc.round_bf16(y))  # output is representable in bf16
     y64 = orc.layer_norm(x, scale, bias, 1e-5, dtype="float64")
     assert np.abs(y - y64).max() < 0.05
+
+
+def test_q_scale_division_equals_multiplication_by_the_rounded_reciprocal():
+    """The projection kernel scales q by multiplying with fl(1 / bf16(sqrt 32)) instead of
+    dividing; for every finite bf16 input both give the same bf16 result (the divisor is
+    181/32, so an exact quotient is never within fp32 rounding error of a bf16 boundary)."""
+    import ml_dtypes
+
+    x = np.arange(0, 1 << 16, dtype=np.uint16).view(ml_dtypes.bfloat16).astype(np.float32)
+    x = x[np.isfinite(x)]
+    y = np.float32(np.float32(np.sqrt(np.float32(32.0))).astype(ml_dtypes.bfloat16))
+    assert float(y) == 181.0 / 32.0
+    inv = np.float32(1.0) / y
+    div = (x / y).astype(np.float32).astype(ml_dtypes.bfloat16).view(np.uint16)
+    mul = (x * inv).astype(np.float32).astype(ml_dtypes.bfloat16).view(np.uint16)
+    assert np.array_equal(div, mul)
