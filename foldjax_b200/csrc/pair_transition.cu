@@ -214,50 +214,14 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool alive = true;
 
-    // Layer norm of one row in place, in three sweeps over shared memory (mean,
-    // variance, normalise) so that it needs few registers; same arithmetic and
-    // rounding points as ln_rows_inplace.
+    // Layer norm of one row in place (the register-light form).
     auto layer_norm_tile = [&](long long it) {
       const int xs = static_cast<int>(it % XSTAGES);
       if (!mbar_wait(&sm.x_full[xs], static_cast<uint32_t>((it / XSTAGES) & 1), p.status, ST_TIMEOUT_PROLOGUE)) {
         alive = false;
         return;
       }
-      uint8_t* tile = sm.x[xs];
-      float sum = 0.f;
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        const uint4 v = *reinterpret_cast<const uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sum += bf16_lo(w[e]) + bf16_hi(w[e]);
-      }
-      const float mean = sum * (1.0f / 128.0f);
-      float sq = 0.f;
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        const uint4 v = *reinterpret_cast<const uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = bf16_lo(w[e]) - mean, b = bf16_hi(w[e]) - mean;
-          sq = fmaf(a, a, sq);
-          sq = fmaf(b, b, sq);
-        }
-      }
-      const float rstd = rsqrtf(sq * (1.0f / 128.0f) + p.eps);
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        uint4* ptr = reinterpret_cast<uint4*>(tile + (c >> 3) * SLAB_BYTES + sw128_offset(row, c & 7));
-        const uint4 v = *ptr;
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = (bf16_lo(w[e]) - mean) * rstd, b = (bf16_hi(w[e]) - mean) * rstd;
-          w[e] = bf16x2_add(bf16x2_mul(pack_bf16x2(a, b), sm.gamma2[4 * c + e]), sm.beta2[4 * c + e]);
-        }
-        *ptr = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      ln_row_sweeps(sm.x[xs], row, sm.gamma2, sm.beta2, p.eps);
       fence_proxy_async();
       mbar_arrive(&sm.xn_full[xs]);
     };

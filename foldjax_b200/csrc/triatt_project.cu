@@ -22,8 +22,8 @@
 //   warp 0      TMA producer (weights once, x tiles in a 3-stage ring)
 //   warp 1      MMA issuer: [q|k] = xn.[Wq|Wk]^T (N=256), bias = xn.Wb^T (N=16),
 //               vT = Wv.xn^T ("transposed": a TMEM lane is a channel)
-//   warps 2-5   layer norm in place (one thread per pair)
-//   warps 6-9   epilogue
+//   warps 2-9   layer norm in place (two threads per pair)
+//   warps 10-13 epilogue
 // TMEM: [q|k] 256 columns, vT 128, bias 16; each group is released on its own
 // so the next tile's MMAs overlap this tile's epilogue.
 // Bound: HBM (read x, write q, k, vT: 4 * n*n*128*2 bytes).
@@ -41,7 +41,8 @@ namespace {
 constexpr int XSTAGES = 3;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
 constexpr int W_BYTES = 8 * SLAB_BYTES;  // rows 0..255 [Wq|Wk], 256..383 Wv, 384..399 Wb, rest zero
-constexpr int THREADS = 320;
+constexpr int LN_WARPS = 8;  // two threads per pair
+constexpr int THREADS = 64 + LN_WARPS * 32 + 128;
 constexpr uint32_t TM_QK = 0, TM_V = 256, TM_B = 384;
 enum { G_QK = 0, G_B = 1, G_V = 2 };
 
@@ -88,7 +89,7 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     mbar_init(&sm.w_full, 1);
     for (int s = 0; s < XSTAGES; ++s) {
       mbar_init(&sm.x_full[s], 1);
-      mbar_init(&sm.xn_full[s], 128);
+      mbar_init(&sm.xn_full[s], LN_WARPS * 32);
       mbar_init(&sm.x_empty[s], 1);
     }
     for (int g = 0; g < 3; ++g) {
@@ -192,16 +193,13 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       }
       (void)idesc_qk;
     }
-  } else if (warp < 6) {
-    const int r = threadIdx.x - 64;
+  } else if (warp < 2 + LN_WARPS) {
+    const int r = (warp - 2) * 16 + (lane & 15);  // pair of the tile; lanes l and l ^ 16 share it
     int stage = 0;
     uint32_t phase = 0;
     for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       if (!mbar_wait(&sm.x_full[stage], phase, p.status, ST_TIMEOUT_PROLOGUE)) break;
-      uint4 v[16];
-      ln_load_row(sm.x[stage], r, v);
-      ln_rows_inplace(v, sm.gamma2, sm.beta2, p.eps);
-      ln_store_row(sm.x[stage], r, v);
+      ln_row_two_threads(sm.x[stage], r, lane >> 4, sm.gamma2, sm.beta2, p.eps);
       fence_proxy_async();
       mbar_arrive(&sm.xn_full[stage]);
       if (++stage == XSTAGES) {

@@ -15,8 +15,8 @@
 // Persistent kernel, one CTA per SM, 10 warps:
 //   warp 0      TMA producer: weights once (128 KiB, resident), x tiles in a 3-stage ring
 //   warp 1      MMA issuer: 4 groups (p_a, g_a, p_b, g_b) of 128x128x128 per tile
-//   warps 2-5   layer norm, in place in the tile TMA delivered (one thread per pair)
-//   warps 6-9   epilogue: TMEM -> sigmoid gate -> mask -> bf16 -> global
+//   warps 2-9   layer norm, in place in the tile TMA delivered (two threads per pair)
+//   warps 10-13 epilogue: TMEM -> sigmoid gate -> mask -> bf16 -> global
 // TMEM: four 128-column accumulators; the a-half and the b-half are released
 // separately so the MMAs of the next tile overlap the epilogue of this one.
 //
@@ -34,7 +34,8 @@ constexpr int XSTAGES = 3;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;  // 32 KiB: 128 pairs x 128 channels bf16
 constexpr int W_BYTES = 8 * SLAB_BYTES;     // 128 KiB: 4 groups x 2 K-slabs
 constexpr int MASK_SLOTS = 4;
-constexpr int THREADS = 320;
+constexpr int LN_WARPS = 8;  // two threads per pair
+constexpr int THREADS = 64 + LN_WARPS * 32 + 128;
 
 struct Smem {
   uint8_t w[W_BYTES];
@@ -80,7 +81,7 @@ project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     mbar_init(&sm.w_full, 1);
     for (int s = 0; s < XSTAGES; ++s) {
       mbar_init(&sm.x_full[s], 1);
-      mbar_init(&sm.xn_full[s], 128);
+      mbar_init(&sm.xn_full[s], LN_WARPS * 32);
       mbar_init(&sm.x_empty[s], 1);
     }
     for (int h = 0; h < 2; ++h) {
@@ -160,9 +161,9 @@ project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         }
       }
     }
-  } else if (warp < 6) {
-    // ---- layer norm, one thread per pair of the tile
-    const int r = threadIdx.x - 64;
+  } else if (warp < 2 + LN_WARPS) {
+    // ---- layer norm, two threads per pair of the tile (lanes l and l ^ 16)
+    const int r = (warp - 2) * 16 + (lane & 15);
     int stage = 0;
     uint32_t phase = 0, it = 0;
     for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
@@ -171,11 +172,8 @@ project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       float mval = 0.f;
       if (t < p.n_inner) mval = p.mask ? p.mask[o * p.ms_outer + t * p.ms_inner] : 1.0f;
       if (!mbar_wait(&sm.x_full[stage], phase, p.status, ST_TIMEOUT_PROLOGUE)) break;
-      uint4 v[16];
-      ln_load_row(sm.x[stage], r, v);
-      ln_rows_inplace(v, sm.gamma2, sm.beta2, p.eps);
-      ln_store_row(sm.x[stage], r, v);
-      sm.mask[it & (MASK_SLOTS - 1)][r] = __float2bfloat16_rn(mval);
+      ln_row_two_threads(sm.x[stage], r, lane >> 4, sm.gamma2, sm.beta2, p.eps);
+      if (lane < 16) sm.mask[it & (MASK_SLOTS - 1)][r] = __float2bfloat16_rn(mval);
       fence_proxy_async();
       mbar_arrive(&sm.xn_full[stage]);
       if (++stage == XSTAGES) {
