@@ -323,9 +323,10 @@ def run_gpu(args) -> None:
         "roofline": {
             "kernel": "att_core_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"{peak_kind} sustained bf16",
-            # dram read + write bytes per launch from the committed ncu capture at N = 1024
-            # (profiles/att_core_n1024_ncu.md); not proportional to N, so null elsewhere
-            "traffic": 1.907e9 if (n == 1024 and world == 1) else None, "avg_launch_ms": core_avg, "launches": core_n,
+            # dram read + write bytes per launch from the committed ncu captures at N = 1024 and
+            # N = 3072 (profiles/att_core_n1024_ncu.md); not proportional to N, so null elsewhere
+            "traffic": {1024: 1.907e9, 3072: 5.55e10}.get(n) if world == 1 else None,
+            "avg_launch_ms": core_avg, "launches": core_n,
             "note": "binding resource is the MUFU/ALU softmax path (4*N^3 exps), not the tensor pipe",
         },
         "pair_transition": {
