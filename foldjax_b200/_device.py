@@ -29,7 +29,7 @@ def workspace(nbytes: int, tag: str = "default") -> torch.Tensor:
     dev = torch.cuda.current_device()
     key = (dev, tag)
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
+    if buf is None or buf.numel() < int(nbytes) + 1024:  # callers round the pointer up by up to 1023 B
         _workspaces.pop(key, None)
         buf = torch.empty(int(nbytes) + 1024, dtype=torch.uint8, device=f"cuda:{dev}")
         _workspaces[key] = buf
@@ -39,6 +39,37 @@ def workspace(nbytes: int, tag: str = "default") -> torch.Tensor:
 def aligned_ptr(buf: torch.Tensor, align: int = 1024) -> int:
     p = buf.data_ptr()
     return (p + align - 1) // align * align
+
+
+def check_out(out: torch.Tensor, like: torch.Tensor, name: str = "out") -> torch.Tensor:
+    """The caller's result buffer goes to the kernels as a raw pointer, so it must be
+    exactly what they write: a contiguous CUDA bf16 tensor of the input's shape on the
+    input's device. Anything else would be a write past the buffer, not a Python error."""
+    if not isinstance(out, torch.Tensor):
+        raise ValueError(f"{name} must be a torch tensor, got {type(out).__name__}")
+    if out.dtype != like.dtype:
+        raise ValueError(f"{name} must be {like.dtype}, got {out.dtype}")
+    if tuple(out.shape) != tuple(like.shape):
+        raise ValueError(f"{name} shape {tuple(out.shape)} does not match the input {tuple(like.shape)}")
+    if not out.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if not out.is_cuda or out.device != like.device:
+        raise ValueError(f"{name} must be a CUDA tensor on the input's device ({like.device}), got {out.device}")
+    return out
+
+
+def check_same_shape(t: torch.Tensor, like: torch.Tensor, name: str) -> torch.Tensor:
+    if tuple(t.shape) != tuple(like.shape):
+        raise ValueError(f"{name} shape {tuple(t.shape)} does not match the input {tuple(like.shape)}")
+    return t
+
+
+def check_device_status() -> None:
+    """Read (and clear) the device status word at a point where the host synchronises
+    anyway; raises if a kernel gave up on a bounded wait since the last check."""
+    from . import _lib
+
+    _lib.device_status()
 
 
 def release_workspaces() -> None:

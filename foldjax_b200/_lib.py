@@ -114,7 +114,7 @@ class TriattCoreArgs(C.Structure):
         ("mask", C.c_void_p), ("ms_i", C.c_int64), ("ms_k", C.c_int64), ("inf", C.c_float),
         ("o", C.c_void_p), ("row_max", C.c_void_p), ("row_sum", C.c_void_p), ("unnormalized", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("acc_o", C.c_void_p), ("resume", C.c_int32),
+        ("acc_o", C.c_void_p), ("resume", C.c_int32), ("mask_additive", C.c_int32),
     ]
 
 
@@ -169,6 +169,7 @@ SIGNATURES = {
     "b200tri_version": (C.c_int, []),
     "b200tri_last_error": (C.c_char_p, []),
     "b200tri_device_status": (C.c_int, []),
+    "b200tri_selftest_wait": (C.c_int, [C.c_int64, C.c_void_p]),
     "b200tri_launch_count": (C.c_uint64, []),
     "b200tri_set_sm_limit": (C.c_int, [C.c_int32]),
     "b200tri_timing_enable": (C.c_int, [C.c_int32]),

@@ -1,15 +1,25 @@
 """Selector glue: makes "b200" a value of FoldJAX's triangle-kernel option surface.
 
 FoldJAX has no single registry object for triangle kernels; the "registry" is a
-set of tables and dispatch sites (src/foldjax/execution.py:40-50 KNOBS,
-src/foldjax/backends/boltz2.py:162-165, protenix.py:181-184, openfold3.py:168-170,
-and the dispatch in boltz2 triangle_attention.py:384-418 / triangle.py:67-76).
-``register(foldjax)`` adds the new value to the tables it finds on an importable
-FoldJAX package and returns what it changed; the dispatch-site edits a maintainer
-makes are listed in INTEGRATION.md. FoldJAX (and JAX) are not installed next to
-this repository, so this module is exercised against a stand-in package in the
-tests. Policy kept from the reference: an unknown value is an error and nothing
-falls back silently (tests/test_execution_vocabulary.py:140-155).
+set of tables and dispatch sites:
+
+* ``foldjax.execution.KNOBS["triangle_kernel"]`` (src/foldjax/execution.py:40-45),
+  the neutral vocabulary ``normalize``/``translate`` check values against;
+* one ``execution_options["triangle_kernel"] = (native option name, {neutral value:
+  native value})`` entry per model backend class: ``Boltz2Backend``
+  (src/foldjax/backends/boltz2.py:160-165), ``ProtenixBackend`` (protenix.py:179-184,
+  native values carry a ``_jit`` suffix) and ``OpenFold3Backend``
+  (openfold3.py:168-170); OpenDDE exposes no such knob on purpose;
+* the dispatch inside the ports (boltz2 triangle_attention.py:384-418 /
+  triangle.py:67-76 and their Protenix / OpenFold3 counterparts), which a
+  maintainer extends with the stubs shown in this repository's integration notes.
+
+``register(foldjax)`` adds the new value to the first two kinds of table on an
+imported FoldJAX package and returns what it changed. The option layer of FoldJAX
+imports without JAX, so the tests run this against the real modules when a FoldJAX
+checkout sits beside this repository (and against a stand-in with the same
+structure otherwise). Policy kept from the reference: an unknown value is an error
+and nothing falls back silently (tests/test_execution_vocabulary.py:140-155).
 """
 
 from __future__ import annotations
@@ -49,27 +59,69 @@ def resolve(value: str | None, allowed: tuple[str, ...] = ("auto", "cueq", "xla"
         return "xla"
 
 
+# model backend module -> the native spelling of the value in that port
+NATIVE_VALUES = {"boltz2": BACKEND, "protenix": BACKEND + "_jit", "openfold3": BACKEND}
+
+
+def _backend_classes(module: ModuleType | Any):
+    """Classes of a ``foldjax.backends.<model>`` module that carry a triangle-kernel entry."""
+    for name, obj in sorted(vars(module).items()):
+        if not isinstance(obj, type):
+            continue
+        table = obj.__dict__.get("execution_options")
+        if isinstance(table, dict) and "triangle_kernel" in table:
+            yield name, obj, table
+
+
 def register(foldjax: ModuleType | Any) -> dict[str, Any]:
-    """Add "b200" to every selector table found on ``foldjax``. Returns a report
-    {site: new value}; raises if no site was found (a silent no-op would hide a
-    layout change upstream)."""
+    """Add "b200" to every triangle-kernel selector table found on ``foldjax``.
+
+    ``foldjax.execution`` and ``foldjax.backends.<model>`` are imported on demand (none
+    of them needs JAX). Returns a report {site: new value}. Raises if the neutral
+    vocabulary or every model table is missing: a silent no-op would hide a layout
+    change upstream. Calling it twice changes nothing the second time."""
+    import importlib
+
     changed: dict[str, Any] = {}
-    execution = getattr(foldjax, "execution", None)
+    pkg = getattr(foldjax, "__name__", "foldjax")
+
+    def sub(name: str):
+        parts = name.split(".")
+        obj: Any = foldjax
+        for part in parts:
+            nxt = getattr(obj, part, None)
+            if nxt is None:
+                try:
+                    nxt = importlib.import_module(f"{getattr(obj, '__name__', pkg)}.{part}")
+                except Exception:
+                    return None
+            obj = nxt
+        return obj
+
+    execution = sub("execution")
     knobs = getattr(execution, "KNOBS", None)
-    if isinstance(knobs, dict) and "triangle_kernel" in knobs:
-        values = tuple(knobs["triangle_kernel"])
-        if BACKEND not in values:
-            knobs["triangle_kernel"] = values + (BACKEND,)
-        changed["execution.KNOBS['triangle_kernel']"] = knobs["triangle_kernel"]
-    backends = getattr(foldjax, "backends", None)
-    for model, suffix in (("boltz2", ""), ("protenix", "_jit"), ("openfold3", "")):
-        mod = getattr(backends, model, None)
-        table = getattr(mod, "TRIANGLE_KERNEL_VALUES", None)
-        if isinstance(table, dict):
-            table.setdefault(BACKEND, BACKEND + suffix)
-            changed[f"backends.{model}.TRIANGLE_KERNEL_VALUES"] = dict(table)
-    if not changed:
-        raise RuntimeError("no triangle-kernel selector table found on the given foldjax package")
+    if not (isinstance(knobs, dict) and "triangle_kernel" in knobs):
+        raise RuntimeError("foldjax.execution.KNOBS['triangle_kernel'] not found: the option layer changed upstream")
+    values = tuple(knobs["triangle_kernel"])
+    if BACKEND not in values:
+        knobs["triangle_kernel"] = values + (BACKEND,)
+    changed["execution.KNOBS['triangle_kernel']"] = knobs["triangle_kernel"]
+
+    models = 0
+    for model, native in NATIVE_VALUES.items():
+        mod = sub(f"backends.{model}")
+        if mod is None:
+            continue
+        for cls_name, _cls, table in _backend_classes(mod):
+            native_name, mapping = table["triangle_kernel"]
+            if mapping.get(BACKEND) != native:
+                mapping = dict(mapping)
+                mapping[BACKEND] = native
+                table["triangle_kernel"] = (native_name, mapping)
+            changed[f"backends.{model}.{cls_name}.execution_options['triangle_kernel']"] = table["triangle_kernel"]
+            models += 1
+    if models == 0:
+        raise RuntimeError("no model backend with a triangle_kernel entry found on the given foldjax package")
     return changed
 
 

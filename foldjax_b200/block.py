@@ -72,7 +72,8 @@ def triangle_block_forward(params: Mapping[str, Any], z: Any, mask: Any | None, 
         out = torch.empty(cur.shape, dtype=torch.bfloat16, pin_memory=True)
     if isinstance(out, np.ndarray):
         out[...] = cur.float().cpu().numpy()
-        return out
-    out.copy_(cur, non_blocking=True)
-    torch.cuda.current_stream().synchronize()
+    else:
+        out.copy_(cur, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    dev.check_device_status()  # raises if a kernel of the block gave up on a bounded wait
     return out

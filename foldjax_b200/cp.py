@@ -190,6 +190,10 @@ def triangle_multiplication_cp(
         mptr = mask.data_ptr() + 4 * (r * n_r * n + c * n_c)
     if out is None:
         out = torch.empty_like(x)
+    else:
+        dev.check_out(out, x)
+    if residual is not None:
+        dev.check_out(residual, x, "residual")
 
     if outgoing:
         # local tiles as m row blocks of n_c rows: [m][128][n_c][ld], k = the tile's columns
@@ -312,6 +316,10 @@ def triangle_attention_cp(
         assert mask.is_cuda and mask.dtype == torch.float32 and tuple(mask.shape) == (n, n) and mask.is_contiguous()
     if out is None:
         out = torch.empty_like(x)
+    else:
+        dev.check_out(out, x)
+    if residual is not None:
+        dev.check_out(residual, x, "residual")
     if starting:
         n_outer, n_inner, xs_o, xs_i, tiles, own = n_r, n_c, n_c * 128, 128, Cc, c
         msgs = triatt_starting_msgs(grid)

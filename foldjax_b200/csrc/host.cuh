@@ -63,7 +63,13 @@ struct Carver {
 
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// SMs the persistent kernels of the current device may use (its SM count, or the limit
+// set for that device with b200tri_set_sm_limit).
 int sm_count();
+
+// Raises a kernel's dynamic shared-memory limit, once per (kernel, device); safe to call
+// from several host threads (one per device under XLA).
+int ensure_smem_limit(const void* kernel, int bytes);
 
 // Launch accounting and optional per-kernel event timing.
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
@@ -74,7 +80,7 @@ struct TimedLaunch {  // brackets the launches made during its lifetime
   int id;
   cudaStream_t stream;
   cudaEvent_t start = nullptr;
-  TimedLaunch(int id, cudaStream_t stream);
+  TimedLaunch(int id, cudaStream_t stream, bool may_time = true);
   ~TimedLaunch();
 };
 

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "host.cuh"
+#include "tc.cuh"
 
 namespace b200 {
 
@@ -41,14 +42,36 @@ int* device_status_word() {
   return cache[dev];
 }
 
-static std::atomic<int> g_sm_limit{0};
+// Per-device settings: XLA drives every device from its own host thread, so a limit or
+// the timing switch set with one device current must not leak to the others.
+constexpr int kMaxDevices = 64;
+static std::atomic<int> g_sm_limit[kMaxDevices];
+static std::atomic<int> g_timing[kMaxDevices];
+
+static int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  return dev;
+}
 
 static int sm_count_device();
 
 int sm_count() {
   const int n = sm_count_device();
-  const int lim = g_sm_limit.load(std::memory_order_relaxed);
+  const int lim = g_sm_limit[current_device_slot()].load(std::memory_order_relaxed);
   return (lim > 0 && lim < n) ? lim : n;
+}
+
+int ensure_smem_limit(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::vector<std::pair<const void*, int>> done;
+  const int dev = current_device_slot();
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto& e : done)
+    if (e.first == kernel && e.second == dev) return B200TRI_OK;
+  B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.emplace_back(kernel, dev);
+  return B200TRI_OK;
 }
 
 static int sm_count_device() {
@@ -65,19 +88,18 @@ static int sm_count_device() {
 }
 
 static std::atomic<uint64_t> g_launches{0};
-static std::atomic<int> g_timing{0};
 static std::mutex g_timing_mu;
 static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events[K_COUNT];
 static const char* const kKernelNames[K_COUNT] = {"trimul_project", "trimul_contract", "trimul_finish",
                                                   "triatt_project", "triatt_core",     "triatt_finish",
                                                   "pair_transition", "pair_bias"};
 
-bool timing_enabled() { return g_timing.load(std::memory_order_relaxed) != 0; }
+bool timing_enabled() { return g_timing[current_device_slot()].load(std::memory_order_relaxed) != 0; }
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
-TimedLaunch::TimedLaunch(int id_, cudaStream_t stream_) : id(id_), stream(stream_) {
-  if (!g_timing.load(std::memory_order_relaxed)) return;
+TimedLaunch::TimedLaunch(int id_, cudaStream_t stream_, bool may_time) : id(id_), stream(stream_) {
+  if (!may_time || !timing_enabled()) return;
   if (cudaEventCreate(&start) != cudaSuccess) {
     start = nullptr;
     return;
@@ -133,21 +155,47 @@ int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int
 
 }  // namespace b200
 
+namespace b200 {
+// One warp waits on an mbarrier that nothing ever arrives at, through the same bounded wait
+// every kernel of the library uses, with a caller-chosen limit.
+__global__ void selftest_wait_kernel(long long limit_cycles, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait_limited(&bar, 0, status, ST_TIMEOUT_SELFTEST, limit_cycles, 0u);
+}
+}  // namespace b200
+
 extern "C" {
+
+int b200tri_selftest_wait(int64_t limit_cycles, b200tri_stream_t stream) {
+  using namespace b200;
+  B200_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, B200TRI_ERR_INVALID,
+               "selftest_wait: limit must be in (0, 2e9] cycles (got %lld)", static_cast<long long>(limit_cycles));
+  int* status = device_status_word();
+  B200_REQUIRE(status != nullptr, B200TRI_ERR_CUDA, "selftest_wait: no current CUDA device");
+  count_launch();
+  selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_cycles, status);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200TRI_OK;
+}
 
 int b200tri_version(void) { return 100; }
 
 const char* b200tri_last_error(void) { return b200::get_error(); }
 
 int b200tri_set_sm_limit(int32_t sms) {
-  b200::g_sm_limit.store(sms > 0 ? sms : 0);
+  b200::g_sm_limit[b200::current_device_slot()].store(sms > 0 ? sms : 0);
   return B200TRI_OK;
 }
 
 uint64_t b200tri_launch_count(void) { return b200::g_launches.load(); }
 
 int b200tri_timing_enable(int32_t on) {
-  b200::g_timing.store(on ? 1 : 0);
+  b200::g_timing[b200::current_device_slot()].store(on ? 1 : 0);
   return B200TRI_OK;
 }
 
@@ -198,7 +246,7 @@ int b200tri_device_status(void) {
   if (v != 0) {
     int zero = 0;
     cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice);
-    b200::set_error("a kernel gave up on a bounded device wait (role code %d)", v);
+    b200::set_error("B200TRI_ERR_TIMEOUT: a kernel gave up on a bounded device wait (role code %d)", v);
   }
   return v;
 }

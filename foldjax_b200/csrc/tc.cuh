@@ -28,6 +28,7 @@ enum : int {
   ST_TIMEOUT_EPILOGUE = 103,
   ST_TIMEOUT_PROLOGUE = 104,
   ST_TIMEOUT_SOFTMAX = 105,
+  ST_TIMEOUT_SELFTEST = 110,  // the wait of b200tri_selftest_wait ran out (as it is meant to)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -89,7 +90,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `status` points at the device status word (global memory).
 // Gives up after WAIT_LIMIT_CYCLES, or as soon as another thread has recorded a
 // failure, so that one stuck role drains the whole CTA quickly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                  long long limit_cycles, uint32_t check_mask) {
   // Fast path: a few plain polls (the hardware parks the thread inside try_wait),
   // no clock reads on the way.
 #pragma unroll 1
@@ -98,14 +100,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0x3f) == 0) {
+    if ((it & check_mask) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != ST_OK) return false;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit_cycles) {
         atomicCAS(status, ST_OK, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_limited(bar, parity, status, code, WAIT_LIMIT_CYCLES, 0x3fu);
 }
 
 // ---------------------------------------------------------------- TMA

@@ -46,6 +46,23 @@ namespace {
 #ifndef B200_TURNS
 #define B200_TURNS 1
 #endif
+// 1: the pair bias is added by the tensor core (S = bias . I + Q . K^T); 0: by the softmax threads.
+#ifndef B200_BIAS_MMA
+#define B200_BIAS_MMA 1
+#endif
+// 1: the exponentials of a step start from the offset of the previous steps while the
+// step's maximum is still being reduced; they are redone when the offset has to move.
+#ifndef B200_SPEC
+#define B200_SPEC 1
+#endif
+// Of every 16 pairs of exponentials, this many are evaluated on the FMA pipe.
+#ifndef B200_POLY
+#define B200_POLY 0
+#endif
+// 1: registers are moved from the control warpgroup to the softmax warpgroups at start-up.
+#ifndef B200_SETMAXNREG
+#define B200_SETMAXNREG 1
+#endif
 constexpr int NWG = B200_NWG;  // softmax warpgroups = rows i that share one bias tile
 constexpr int KT = 64;
 constexpr int STAGES = 3;
@@ -71,6 +88,9 @@ constexpr float MASKED_SCORE = -30000.0f;
 struct Smem {
   uint8_t q[NWG][Q_BYTES];
   uint8_t bias[STAGES][BIAS_BYTES];
+#if B200_BIAS_MMA
+  uint8_t ident[KT * 128];  // 64 x 64 bf16 identity, K-major rows of 128 B under the 128-byte swizzle
+#endif
   uint8_t k[STAGES][NWG][K_BYTES];
   uint8_t v[STAGES][NWG][V_BYTES];
   float mb[STAGES][NWG][KT];
@@ -100,6 +120,22 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) { return umma_des
 
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
   return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// 2^t for a pair on the FMA pipe: t = n + f with n the nearest integer (taken from the low
+// mantissa bits after adding 1.5 * 2^23) and |f| <= 0.5; a cubic for 2^f (2e-4 relative, below
+// the fp16 rounding P gets anyway); n goes straight into the exponent field. Inputs below -120
+// (masked and padded keys) are clamped and round to zero as fp16.
+__device__ __forceinline__ float2 poly_exp2x2(float2 t) {
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);
+  t = make_float2(fmaxf(t.x, -120.0f), fmaxf(t.y, -120.0f));
+  const float2 y = __fadd2_rn(t, magic);
+  const float2 f = __fadd2_rn(t, __fadd2_rn(magic, make_float2(-y.x, -y.y)));
+  float2 q = __ffma2_rn(make_float2(0.05286743f, 0.05286743f), f, make_float2(0.24215189f, 0.24215189f));
+  q = __ffma2_rn(q, f, make_float2(0.69358677f, 0.69358677f));
+  q = __ffma2_rn(q, f, make_float2(0.99996275f, 0.99996275f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(y.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(y.y) << 23)));
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -147,6 +183,20 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.v[0][0][0] + tile * V_BYTES + V_TMA_BYTES);
     dst[w] = (w < 32) ? 0x3C003C00u : 0u;  // fp16 1.0 pairs in row 32
   }
+#if B200_BIAS_MMA
+  // The bias tile of a step is itself a K-major A operand ([128 queries][64 keys]); multiplied
+  // by this identity it lands in the score accumulator exactly (bf16 x 1.0 in fp32), so the
+  // softmax threads never touch the bias.
+  for (int idx = threadIdx.x; idx < KT * 128 / 4; idx += blockDim.x) {
+    const int row = idx / 32, w = idx % 32;          // 32-bit word w of the row = elements 2w, 2w+1
+    const int chunk = (w >> 2) ^ (row & 7);          // undo the swizzle: logical 16-byte chunk
+    const int e0 = chunk * 8 + (w & 3) * 2;          // logical element index of the low half
+    uint32_t val = 0u;
+    if (e0 == row) val = 0x00003F80u;                // bf16 1.0 in the low half
+    if (e0 + 1 == row) val = 0x3F800000u;
+    reinterpret_cast<uint32_t*>(sm.ident)[idx] = val;
+  }
+#endif
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();
@@ -154,6 +204,15 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = sm.tmem_base;
   const int items_per_head = p.groups * p.tiles_j;
 
+#if B200_SETMAXNREG
+  // The control warpgroup needs few registers; the softmax warpgroups hold 64 scores per
+  // thread and want more than the 128 an even split of the register file gives them.
+#endif
+
+  if (warp < 4) {
+#if B200_SETMAXNREG
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+#endif
   if (warp == 0) {
     if (elect_one()) {
       int stage = 0;
@@ -213,7 +272,17 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint64_t adesc = desc_sw64(smem_u32(sm.q[wg]));
             const uint64_t bdesc = desc_sw64(smem_u32(sm.k[stage][wg]));
             const uint32_t d = tmem_base + wg * TM_WG + TM_S;
+#if B200_BIAS_MMA
+            const uint64_t biasdesc = desc_sw128(smem_u32(sm.bias[stage]));
+            const uint64_t identdesc = desc_sw128(smem_u32(sm.ident));
+#pragma unroll
+            for (int kk = 0; kk < KT / 16; ++kk)
+              umma_bf16_ss(d, umma_desc_advance(biasdesc, kk * 32), umma_desc_advance(identdesc, kk * 32), idesc_qk,
+                           kk != 0);
+            umma_bf16_ss(d, adesc, bdesc, idesc_qk, 1);
+#else
             umma_bf16_ss(d, adesc, bdesc, idesc_qk, 0);
+#endif
             umma_bf16_ss(d, umma_desc_advance(adesc, 32), umma_desc_advance(bdesc, 32), idesc_qk, 1);
             umma_commit(&sm.s_full[wg]);
           }
@@ -262,8 +331,12 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
     // ------------------------------------------------------------- softmax
+#if B200_SETMAXNREG
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+#endif
     const int wg = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // query inside the tile = TMEM lane
@@ -322,6 +395,18 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // fp32 values per instruction (add/fma .f32x2), halving the softmax's ALU work.
         float2 u[KT / 2];
         {
+#if B200_BIAS_MMA
+          // q.k + bias arrives from the tensor core; both halves are requested at once.
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_wg + TM_S, r0);
+          tmem_ld32(t_wg + TM_S + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            u[e] = make_float2(__uint_as_float(r0[2 * e]), __uint_as_float(r0[2 * e + 1]));
+            u[16 + e] = make_float2(__uint_as_float(r1[2 * e]), __uint_as_float(r1[2 * e + 1]));
+          }
+#else
           // Two halves of 32 keys: the TMEM load of the second half and the bias
           // fetches overlap the adds of the first, and at most one raw half is live.
           const uint8_t* brow = sm.bias[stage];
@@ -350,6 +435,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tmem_ld_wait();
             }
           }
+#endif
           tc_fence_before();
           mbar_arrive(&sm.s_free[wg]);
         }
@@ -370,25 +456,6 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.st_empty[stage]);
-        // four independent chains, so the reduction is not one 32-deep dependency
-        float mxa = fmaxf(u[0].x, u[0].y), mxb = fmaxf(u[1].x, u[1].y);
-        float mxc = fmaxf(u[2].x, u[2].y), mxd = fmaxf(u[3].x, u[3].y);
-#pragma unroll
-        for (int e = 4; e < KT / 2; e += 4) {
-          mxa = fmax3(mxa, u[e].x, u[e].y);
-          mxb = fmax3(mxb, u[e + 1].x, u[e + 1].y);
-          mxc = fmax3(mxc, u[e + 2].x, u[e + 2].y);
-          mxd = fmax3(mxd, u[e + 3].x, u[e + 3].y);
-        }
-        const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
-        const float m_new = fmaxf(m_run, mx);
-        m_run = m_new;
-        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
-        float alpha = 1.f;
-        if (need) {
-          alpha = fast_exp2((m_used - m_new) * LOG2E);  // 0 on the first step (m_used = -inf)
-          m_used = m_new;
-        }
         // P buffer free and O stable once the previous step's P.V has completed (it
         // was issued before this step's Q.K^T, so this wait does not stall).
         if (!mbar_wait(&sm.pv_done[wg], (g & 1) ^ 1, p.status, ST_TIMEOUT_SOFTMAX)) {
@@ -413,27 +480,72 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // for the keys that equal the offset).
         // P goes to TMEM in two halves of 32 keys to keep the live registers down.
         const float2 log2e2 = make_float2(LOG2E, LOG2E);
-        const float nm = -m_used * LOG2E;
-        const float2 nm2 = make_float2(nm, nm);
+        auto emit_p = [&](float offset) {
+          const float nm = -offset * LOG2E;
+          const float2 nm2 = make_float2(nm, nm);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t packed[16];
+          for (int half = 0; half < 2; ++half) {
+            uint32_t packed[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float2 ue = u[16 * half + e];
-            const float2 t2 = __ffma2_rn(ue, log2e2, nm2);
-            // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
-            // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
-            const __half2 h2 = __floats2half2_rn(fast_exp2(t2.x), fast_exp2(t2.y));
-            packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            for (int e = 0; e < 16; ++e) {
+              const float2 ue = u[16 * half + e];
+              const float2 t2 = __ffma2_rn(ue, log2e2, nm2);
+              float2 ex;
+              if (e >= 16 - B200_POLY) {
+                ex = poly_exp2x2(t2);
+              } else {
+                ex = make_float2(fast_exp2(t2.x), fast_exp2(t2.y));
+              }
+              // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
+              // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
+              const __half2 h2 = __floats2half2_rn(ex.x, ex.y);
+              packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            tmem_st16(t_wg + TM_P + 16 * half, packed);
           }
-          tmem_st16(t_wg + TM_P + 16 * half, packed);
+        };
+#if B200_SPEC
+        // Nothing in the exponentials below depends on this step's maximum: they use the
+        // offset the earlier steps settled on, so the MUFU work, the packed fmas and the
+        // max reduction are independent instruction streams the scheduler can interleave.
+        // The offset only has to move when the maximum grew past the rescale threshold,
+        // which is rare after the first step of an item; then the step's P is redone.
+        const bool have_offset = (t > 0) || p.resume;
+        if (have_offset) emit_p(m_used);
+#endif
+        // four independent chains, so the reduction is not one 32-deep dependency
+        float mxa = fmaxf(u[0].x, u[0].y), mxb = fmaxf(u[1].x, u[1].y);
+        float mxc = fmaxf(u[2].x, u[2].y), mxd = fmaxf(u[3].x, u[3].y);
+#pragma unroll
+        for (int e = 4; e < KT / 2; e += 4) {
+          mxa = fmax3(mxa, u[e].x, u[e].y);
+          mxb = fmax3(mxb, u[e + 1].x, u[e + 1].y);
+          mxc = fmax3(mxc, u[e + 2].x, u[e + 2].y);
+          mxd = fmax3(mxd, u[e + 3].x, u[e + 3].y);
         }
+        const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+        const float m_new = fmaxf(m_run, mx);
+        m_run = m_new;
+        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
+        float alpha = 1.f;
+        if (need) {
+          alpha = fast_exp2((m_used - m_new) * LOG2E);  // 0 on the first step (m_used = -inf)
+          m_used = m_new;
+        }
+        const bool any_need = __any_sync(0xffffffffu, need);
+#if B200_SPEC
+        if (!have_offset || any_need) {
+          if (have_offset) tmem_st_wait();  // the speculative P is overwritten in order
+          emit_p(m_used);
+        }
+#else
+        emit_p(m_used);
+#endif
 #if B200_TURNS
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.turn[(wg + 1) % NWG][quarter]);
 #endif
-        if ((t > 0 || p.resume) && __any_sync(0xffffffffu, need)) {
+        if ((t > 0 || p.resume) && any_need) {
           uint32_t o[32];
           tmem_ld32(t_wg + TM_O, o);
           tmem_ld_wait();
@@ -503,12 +615,19 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // padding (keys that do not exist), built in fp32 like the reference
 // (triangle_attention.py:138-142).
 __global__ void mask_bias_kernel(const float* __restrict__ mask, long long ms_i, long long ms_k, int n_i, int n_k,
-                                 int ld, float inf, float* __restrict__ out) {
+                                 int ld, float inf, int additive, float* __restrict__ out) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(n_i) * ld) return;
   const int i = static_cast<int>(idx / ld), k = static_cast<int>(idx % ld);
   float v = -INFINITY;
-  if (k < n_k) v = mask ? fmaxf(inf * (mask[i * ms_i + k * ms_k] - 1.0f), MASKED_SCORE) : 0.0f;
+  if (k < n_k && mask) {
+    const float m = mask[i * ms_i + k * ms_k];
+    // fmaxf drops a NaN operand, so a NaN bias would silently become "keep": map it to "drop"
+    const float b = additive ? m : inf * (m - 1.0f);
+    v = (b == b) ? fmaxf(b, MASKED_SCORE) : MASKED_SCORE;
+  } else if (k < n_k) {
+    v = 0.0f;
+  }
   out[idx] = v;
 }
 
@@ -520,7 +639,18 @@ extern "C" size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k) 
   return static_cast<size_t>(n_i) * b200::round_up(n_k, 64) * sizeof(float) + 1024;
 }
 
-extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_stream_t stream_) {
+namespace {
+// `may_time` = false keeps the launch free of event creation whatever the timing switch
+// says at that moment (the allocation-free entry point relies on it).
+int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, bool may_time);
+}  // namespace
+
+extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_stream_t stream) {
+  return core_launch(a, stream, true);
+}
+
+namespace {
+int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, bool may_time) {
   using namespace b200;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "att core: null args");
@@ -551,7 +681,7 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
     const long long total = static_cast<long long>(a->n_i) * ldm;
     count_launch();
     mask_bias_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-        a->mask, a->ms_i, a->ms_k, a->n_i, a->n_k, ldm, a->inf, mb);
+        a->mask, a->ms_i, a->ms_k, a->n_i, a->n_k, ldm, a->inf, a->mask_additive ? 1 : 0, mb);
     B200_CUDA_OK(cudaGetLastError());
   }
 
@@ -608,22 +738,20 @@ extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_st
   p.resume = a->resume ? 1 : 0;
   p.status = status;
 
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    B200_CUDA_OK(cudaFuncSetAttribute(att_core_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-    configured[dev & 63] = true;
+  {
+    const int rc = ensure_smem_limit(reinterpret_cast<const void*>(att_core_kernel), (int)sizeof(Smem));
+    if (rc) return rc;
   }
   const long long grid = p.total_items < sm_count() ? p.total_items : sm_count();
   {
-    TimedLaunch timed(K_TRIATT_CORE, stream);
+    TimedLaunch timed(K_TRIATT_CORE, stream, may_time);
     count_launch();
     att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm_k, tm_v, tm_b, tm_m, p);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
 }
+}  // namespace
 
 // ---------------------------------------------------------------------------
 // Variant for callers that cannot provide scratch memory and must not allocate:
@@ -674,5 +802,5 @@ extern "C" int b200tri_triatt_core_static(const b200tri_triatt_core_args* a, b20
   b200tri_triatt_core_args local = *a;
   local.workspace = scratch;
   local.workspace_bytes = sizeof(float) * static_cast<size_t>(B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS + 256);
-  return b200tri_triatt_core(&local, stream);
+  return core_launch(&local, stream, false);
 }

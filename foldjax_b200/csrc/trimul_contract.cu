@@ -312,12 +312,9 @@ extern "C" int b200tri_trimul_contract(const b200tri_trimul_contract_args* a, b2
   p.out_block_stride = a->out_block_stride;
   p.status = status;
 
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    B200_CUDA_OK(cudaFuncSetAttribute(contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured[dev & 63] = true;
+  {
+    const int rc = ensure_smem_limit(reinterpret_cast<const void*>(contract_kernel), SMEM_BYTES);
+    if (rc) return rc;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   {

@@ -314,12 +314,9 @@ extern "C" int b200tri_trimul_finish(const b200tri_trimul_finish_args* a, b200tr
   p.t_rpb = (a->t_rows_per_block > 0 && a->t_rows_per_block < a->n_i) ? a->t_rows_per_block : a->n_i;
   p.status = status;
 
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    B200_CUDA_OK(cudaFuncSetAttribute(finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-    configured[dev & 63] = true;
+  {
+    const int rc = ensure_smem_limit(reinterpret_cast<const void*>(finish_kernel), (int)sizeof(Smem));
+    if (rc) return rc;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   {

@@ -326,12 +326,9 @@ extern "C" int b200tri_trimul_project(const b200tri_trimul_project_args* a, b200
   p.eps = a->eps;
   p.status = status;
 
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    B200_CUDA_OK(cudaFuncSetAttribute(project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-    configured[dev & 63] = true;
+  {
+    const int rc = ensure_smem_limit(reinterpret_cast<const void*>(project_kernel), (int)sizeof(Smem));
+    if (rc) return rc;
   }
   const long long grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   {

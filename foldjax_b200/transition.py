@@ -62,8 +62,8 @@ def transition_forward(
             raise ValueError(f"residual shape {tuple(rd.shape)} does not match x {tuple(xd.shape)}")
     if out is None:
         out = torch.empty_like(xd)
-    elif out.shape != xd.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
-        raise ValueError("out must be a contiguous bf16 tensor shaped like x")
+    else:
+        dev.check_out(out, xd)
     if out.data_ptr() == xd.data_ptr() and (rd is None or rd.data_ptr() != xd.data_ptr()):
         raise ValueError("out may alias x only when x is also the residual")
     leaves = {
@@ -92,5 +92,6 @@ def transition_forward(
     _lib.check(lib.b200tri_pair_transition(C.byref(args), C.c_void_p(dev.stream_ptr())))
     if host_in:
         host = out.float().cpu() if numpy_in else out.cpu()
+        dev.check_device_status()
         return host.numpy() if numpy_in else host
     return out

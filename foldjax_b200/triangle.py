@@ -92,10 +92,13 @@ def triangle_multiplication_forward(
     rd = None
     if residual is not None:
         rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+        dev.check_same_shape(rd, xd, "residual")
     if out is None:
         out = torch.empty_like(xd)
     else:
-        out, _ = _check_pair(out)
+        if isinstance(out, torch.Tensor) and out.dim() == 3:
+            out = out.unsqueeze(0)
+        dev.check_out(out, xd)
     leaves = {
         "norm_in_scale": _leaf(params, "norm_in", "scale"),
         "norm_in_bias": _leaf(params, "norm_in", "bias"),
@@ -122,5 +125,6 @@ def triangle_multiplication_forward(
     result = out[0] if squeeze else out
     if host_in:
         host = result.float().cpu() if numpy_in else result.cpu()
+        dev.check_device_status()  # the copy synchronised: a kernel that gave up on a wait shows here
         return host.numpy() if numpy_in else host
     return result

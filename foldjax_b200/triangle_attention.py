@@ -67,10 +67,13 @@ def triangle_attention_forward(
     rd = None
     if residual is not None:
         rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+        dev.check_same_shape(rd, xd, "residual")
     if out is None:
         out = torch.empty_like(xd)
     else:
-        out, _ = _check_pair(out)
+        if isinstance(out, torch.Tensor) and out.dim() == 3:
+            out = out.unsqueeze(0)
+        dev.check_out(out, xd)
     leaves = {
         "norm_scale": _leaf(params, "layer_norm", "scale"),
         "norm_bias": _leaf(params, "layer_norm", "bias"),
@@ -97,6 +100,7 @@ def triangle_attention_forward(
     result = out[0] if squeeze else out
     if host_in:
         host = result.float().cpu() if numpy_in else result.cpu()
+        dev.check_device_status()  # the copy synchronised: a kernel that gave up on a wait shows here
         return host.numpy() if numpy_in else host
     return result
 
@@ -104,13 +108,20 @@ def triangle_attention_forward(
 def attention_core(q, k, v, tri_bias, mask_bias, scale: float | None = None):
     """The attention-core operator: ``core(q, k, v, tri_bias, mask_bias[, scale]) -> out``.
 
-    q/k/v ``[B, I, H, J, D]`` device bf16 tensors (q pre-scaled unless ``scale`` is
-    given, the cuEquivariance convention), ``tri_bias [B, 1, H, J, J]``,
-    ``mask_bias [B, I, 1, 1, J]`` additive fp32 (0 / -inf constant). Returns
-    ``[B, I, H, J, D]`` in ``v.dtype``. Leading axes beyond five are folded into B.
-    This entry re-lays the operands out for the kernel (q,k -> [I,J,H*D], v ->
-    [I,H*D,J] fp16, bias -> [H,J,J]); the module-level forward avoids those copies
-    by producing that layout directly.
+    q/k/v ``[B, I, H, J, D]`` device tensors (q pre-scaled unless ``scale`` is given, the
+    cuEquivariance convention of src/foldjax/models/_cueq.py:66-121: q is then multiplied by
+    ``scale`` cast to q's dtype and the product rounded to that dtype, as the reference's
+    Protenix path does, triangle.py:563,792), ``tri_bias [B, 1, H, J, K]``, ``mask_bias
+    [B, I, 1, 1, K]`` additive fp32 (0, a soft bias, -1e9 or -inf). Returns ``[B, I, H, J, D]``
+    in ``v.dtype``. Leading axes beyond five are folded into B.
+
+    The additive mask bias goes to the kernel as it is (no round trip through a 0/1 mask), so
+    soft and hard entries can be mixed; a row with no kept key comes out as the uniform average
+    over its keys, the convention of the finite -1e9 mask (triangle_attention.py:138-142), not as
+    the zeros of the reference's 2-D ring (src/foldjax/models/_cp_attention.py:380-385).
+    Enqueue-only: nothing here waits for the device. The operands are re-laid out for the
+    kernel with torch copies (q,k -> [I,J,H*D], v -> [I,H*D,K] fp16, bias -> [H,J,K]); the
+    module-level forward avoids those copies by producing that layout directly.
     """
     dev.require_cuda()
     lib = _lib.load()
@@ -124,34 +135,30 @@ def attention_core(q, k, v, tri_bias, mask_bias, scale: float | None = None):
     n_k = kf.shape[-2]
     if (h, d) != (HEADS, HEAD_DIM):
         raise ValueError(f"libb200tri is built for 4 heads x 32; got {h} x {d}")
+    if tuple(mf.shape[1:]) != (n_i, 1, 1, n_k) or tuple(bf.shape[1:]) != (1, h, n_j, n_k):
+        raise ValueError(f"mask_bias {tuple(mask_bias.shape)} / tri_bias {tuple(tri_bias.shape)} do not match "
+                         f"q {tuple(q.shape)} and k {tuple(k.shape)}")
+    qf = qf.to(torch.bfloat16)
     if scale is not None:
-        qf = (qf.float() * float(scale)).to(torch.bfloat16)
+        qf = qf * torch.tensor(float(scale), dtype=torch.bfloat16, device=qf.device)  # one bf16 rounding
     ld = (n_k + 63) // 64 * 64
     out = torch.empty((bsz, n_i, h, n_j, d), dtype=v.dtype, device=v.device)
     nbytes = lib.b200tri_triatt_core_workspace_bytes(n_i, n_k)
     ws = dev.workspace(nbytes, "triatt_core")
     for bi in range(bsz):
-        q2 = qf[bi].permute(0, 2, 1, 3).reshape(n_i, n_j, h * d).to(torch.bfloat16).contiguous()
+        q2 = qf[bi].permute(0, 2, 1, 3).reshape(n_i, n_j, h * d).contiguous()
         k2 = kf[bi].permute(0, 2, 1, 3).reshape(n_i, n_k, h * d).to(torch.bfloat16).contiguous()
         v2 = torch.zeros(n_i, h * d, ld, dtype=torch.float16, device=v.device)
         v2[:, :, :n_k] = vf[bi].permute(0, 1, 3, 2).reshape(n_i, h * d, n_k).to(torch.float16)
         b2 = torch.zeros(h, n_j, ld, dtype=torch.bfloat16, device=v.device)
         b2[:, :, :n_k] = bf[bi, 0].to(torch.bfloat16)
-        # additive mask -> the multiplicative form the kernel takes, with inf = the largest
-        # finite |mask_bias|; -inf entries (the ring tests' spelling of a dropped key) become
-        # mask 0. A row with no valid key comes out as the uniform average over its keys,
-        # the model-level convention of the finite -1e9 mask (triangle_attention.py:138-142).
         mb = mf[bi, :, 0, 0, :].float().contiguous()
-        finite = torch.isfinite(mb)
-        big = float(mb[finite].abs().max().item()) if bool(finite.any()) else 0.0
-        big = big if big > 0 else 1e9
-        m01 = torch.where(finite, 1.0 + mb / big, torch.zeros_like(mb)).contiguous()
         o2 = torch.empty(n_i, n_j, h * d, dtype=torch.bfloat16, device=v.device)
         args = _lib.TriattCoreArgs(
             n_i=n_i, n_j=n_j, n_k=n_k, heads=h, head_dim=d,
             q=q2.data_ptr(), k=k2.data_ptr(), vt=v2.data_ptr(), v_ld=ld,
             bias=b2.data_ptr(), bias_ld=ld, bias_head_stride=n_j * ld,
-            mask=m01.data_ptr(), ms_i=n_k, ms_k=1, inf=big,
+            mask=mb.data_ptr(), ms_i=n_k, ms_k=1, inf=0.0, mask_additive=1,
             o=o2.data_ptr(), row_max=None, row_sum=None, unnormalized=0,
             workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
         )

@@ -43,6 +43,18 @@ const char* b200tri_last_error(void);
  * >100 = the role whose bounded wait ran out) and clears it. */
 int b200tri_device_status(void);
 
+/* Failure-detection self-test. Every wait inside the library's kernels (on an mbarrier
+ * fed by TMA, by the tensor core or by another warp) is bounded: when it runs out, the
+ * kernel records which role gave up in the device status word, drains, frees its tensor
+ * memory and returns, so the context stays usable and the host learns of it from
+ * b200tri_device_status(). This entry exercises that path on purpose and harmlessly: it
+ * enqueues a one-warp kernel that waits, through the same code, on a barrier nothing ever
+ * arrives at, for at most `limit_cycles` SM clock cycles (about 2e6 per millisecond). The
+ * next b200tri_device_status() then reports code 110 and clears it. The reference's
+ * counterpart is the host-side refusal of a half-delivered exchange
+ * (src/foldjax/models/_cp.py:199-256); it has no device-side waits of its own. */
+int b200tri_selftest_wait(int64_t limit_cycles, b200tri_stream_t stream);
+
 /* Measurement aids (not on the data path).
  * b200tri_launch_count: kernels launched by this library in this process so far.
  * b200tri_timing_enable(1): from now on the library brackets each of its main
@@ -53,8 +65,10 @@ int b200tri_device_status(void);
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
 /* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
- * them use at most n SMs (0 = all), which leaves SMs to a communication library
- * whose kernels run beside them (NCCL send/recv during a tile exchange). */
+ * them use at most n SMs (0 = all) on the CURRENT device, which leaves SMs to a
+ * communication library whose kernels run beside them (NCCL send/recv during a tile
+ * exchange). The limit and the timing switch below are kept per device, so host threads
+ * that each drive one device do not disturb one another. */
 int b200tri_set_sm_limit(int32_t sms);
 int b200tri_timing_enable(int32_t on);
 int b200tri_timing_reset(void);
@@ -284,6 +298,12 @@ typedef struct {
    * tile: resume only, which writes the normalised o. */
   float* acc_o;
   int32_t resume;
+  /* 0: `mask` holds 1 (keep) / 0 (drop) and the kernel forms inf * (mask - 1), the way
+   * triangle_attention_forward builds its mask bias (triangle_attention.py:138-142).
+   * 1: `mask` already is the additive mask bias [n_i][n_k] the reference's attention-core
+   * operators receive (0, a soft negative bias, -1e9 or -infinity); `inf` is ignored.
+   * Either way a bias at or below -30000 drops the key. */
+  int32_t mask_additive;
 } b200tri_triatt_core_args;
 
 size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k);

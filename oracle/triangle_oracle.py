@@ -254,6 +254,105 @@ def triangle_attention(
     return out
 
 
+# ---------------------------------------------- sampled elements of large cases
+def triangle_multiplication_sampled(
+    params: Params,
+    xi: np.ndarray,
+    mi: np.ndarray | None,
+    xj: np.ndarray,
+    mj: np.ndarray | None,
+    xij: np.ndarray,
+    eps: float = 1e-5,
+    dtype: str = "float64",
+) -> np.ndarray:
+    """Elements ``update[i_r, j_s, :]`` of triangle_multiplication (triangle.py:78-129)
+    for sampled rows i_r and columns j_s, without forming the whole tensor.
+
+    ``out[i, j] = sum_k a[i, k] * b[j, k]`` (outgoing) needs only rows i and j of the
+    input; the incoming direction is the same sum over the transposed input. So the
+    caller passes, in the frame where k runs along axis 1,
+
+        xi [R, N, C], mi [R, N]   x[i_r, :] and its mask row  (incoming: x[:, i_r], mask[:, i_r])
+        xj [S, N, C], mj [S, N]   x[j_s, :]                   (incoming: x[:, j_s], mask[:, j_s])
+        xij [R, S, C]             x[i_r, j_s], the pair the output gate is computed from
+
+    and gets ``[R, S, C]``. Same rounding points as the full restatement."""
+    pr = _Prec(dtype)
+
+    def project(x, m):
+        xn = layer_norm(x, params["norm_in"]["scale"], params["norm_in"]["bias"], eps, dtype)
+        gate = pr.r(_sigmoid(_linear(xn, params["g_in"]["kernel"], pr)))
+        proj = pr.r(gate * _linear(xn, params["p_in"]["kernel"], pr))
+        if m is not None:
+            proj = pr.r(proj * pr.arr(m)[..., None])
+        return proj.astype(pr.work)
+
+    c = np.asarray(params["p_out"]["kernel"]).shape[0]
+    a = project(xi, mi)[..., :c]  # a = first half of the projection  :102
+    b = project(xj, mj)[..., c:]
+    out = pr.r(np.einsum("rkd,skd->rsd", a, b, optimize=True))  # :231 / :239, :124
+    out = layer_norm(out, params["norm_out"]["scale"], params["norm_out"]["bias"], eps, dtype)
+    out = _linear(out, params["p_out"]["kernel"], pr)
+    x_in = layer_norm(xij, params["norm_in"]["scale"], params["norm_in"]["bias"], eps, dtype)
+    g = pr.r(_sigmoid(_linear(x_in, params["g_out"]["kernel"], pr)))
+    return pr.r(out * g)
+
+
+def triangle_attention_sampled(
+    params: Params,
+    xi: np.ndarray,
+    mi: np.ndarray | None,
+    xj: np.ndarray,
+    cols: np.ndarray,
+    inf: float = 1e9,
+    eps: float = 1e-5,
+    dtype: str = "float64",
+) -> np.ndarray:
+    """Elements ``update[i_r, j_s, :]`` of the starting-node triangle attention
+    (triangle_attention.py:79-162, 346-455) for sampled rows i_r and queries j_s.
+
+    Row i attends over the keys of its own row with the bias ``LN(x)[j, k] @ W``, so the
+    sampled elements need only rows i_r and j_s of the input:
+
+        xi [R, N, C], mi [R, N]   x[i_r, :] and mask[i_r, :]   (ending node: x[:, i_r], mask[:, i_r])
+        xj [S, N, C]              x[j_s, :]                    (ending node: x[:, j_s])
+        cols [S]                  the indices j_s (the queries inside row i)
+
+    Returns ``[R, S, C]``."""
+    pr = _Prec(dtype)
+    work = pr.work
+    cols = np.asarray(cols)
+    xn_i = layer_norm(pr.arr(xi), params["layer_norm"]["scale"], params["layer_norm"]["bias"], eps, dtype)
+    xn_j = layer_norm(pr.arr(xj), params["layer_norm"]["scale"], params["layer_norm"]["bias"], eps, dtype)
+    n = xn_i.shape[1]
+    m = np.ones(xn_i.shape[:2], dtype=np.float32) if mi is None else np.asarray(mi, dtype=np.float32)
+    mask_bias = (np.float32(inf) * (m - np.float32(1.0))).astype(work)  # [R, K]
+    tri_bias = np.transpose(_linear(xn_j, params["linear"]["kernel"], pr), (2, 0, 1))  # [H, S, K]
+    heads = tri_bias.shape[0]
+    mha = params["mha"]
+    c_hidden = np.asarray(mha["linear_g"]["kernel"]).shape[-1] // heads
+    xq = xn_i[:, cols]  # [R, S, C]: the sampled queries of every sampled row
+    qg = _linear(xq, np.concatenate((mha["linear_q"]["kernel"], mha["linear_g"]["kernel"]), axis=-1), pr)
+    q, gate = np.split(qg, 2, axis=-1)
+    kv = _linear(xn_i, np.concatenate((mha["linear_k"]["kernel"], mha["linear_v"]["kernel"]), axis=-1), pr)
+    k, v = np.split(kv, 2, axis=-1)
+    split = lambda t: np.swapaxes(t.reshape(t.shape[:-1] + (heads, c_hidden)), -2, -3)  # [R, H, *, D]
+    q, k, v = split(q), split(k), split(v)
+    q_scale = pr.r(np.sqrt(np.asarray(c_hidden, dtype=work)))
+    q = pr.r(q / q_scale).astype(work)
+    scores = np.matmul(q, np.swapaxes(k.astype(work), -1, -2))  # [R, H, S, K]
+    scores = scores + mask_bias[:, None, None, :] + tri_bias[None].astype(work)
+    scores = scores - scores.max(axis=-1, keepdims=True)
+    p = np.exp(scores)
+    p /= p.sum(axis=-1, keepdims=True)
+    o = pr.r(np.matmul(p, v.astype(work)))  # [R, H, S, D]
+    o = np.swapaxes(o, -2, -3)  # [R, S, H, D]
+    g = pr.r(_sigmoid(gate)).reshape(gate.shape[:-1] + (heads, c_hidden))
+    o = pr.r(o * g).reshape(o.shape[:-2] + (heads * c_hidden,))
+    assert o.shape[1] == len(cols) and n == xn_j.shape[1]
+    return _linear(o, mha["linear_o"]["kernel"], pr)
+
+
 # ------------------------------------------------------------- pair transition
 def transition(params: Params, x: np.ndarray, eps: float = 1e-5, dtype: str = "float64") -> np.ndarray:
     """transition.py:99-112 (the unchunked XLA branch): LN, one matmul against

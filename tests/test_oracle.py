@@ -116,3 +116,45 @@ def test_q_scale_division_equals_multiplication_by_the_rounded_reciprocal():
     div = (x / y).astype(np.float32).astype(ml_dtypes.bfloat16).view(np.uint16)
     mul = (x * inv).astype(np.float32).astype(ml_dtypes.bfloat16).view(np.uint16)
     assert np.array_equal(div, mul)
+
+
+@pytest.mark.parametrize("dtype", ["float64", "bfloat16"])
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+def test_sampled_trimul_elements_equal_the_full_restatement(direction, dtype):
+    """The element-sampling form used for the large GPU cases is the same arithmetic."""
+    rng = np.random.default_rng(31)
+    n = 40
+    params = orc.round_params(orc.random_trimul_params(rng, ln_noise=0.1, std=0.05), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    mask = orc.pad_mask(n, 3)
+    full = orc.triangle_multiplication(params, x, mask, direction, dtype=dtype)[0]
+    rows, cols = np.array([0, 17, 38]), np.array([1, 5, 22, 39])
+    xt, mt = (x[0], mask[0]) if direction == "outgoing" else (x[0].transpose(1, 0, 2), mask[0].T)
+    got = orc.triangle_multiplication_sampled(params, xt[rows], mt[rows], xt[cols], mt[cols],
+                                              x[0][np.ix_(rows, cols)], dtype=dtype)
+    ref = full[np.ix_(rows, cols)]
+    if dtype == "float64":
+        np.testing.assert_allclose(got, ref, rtol=1e-10, atol=1e-12)
+    else:  # a different summation order inside BLAS may flip isolated bf16 roundings
+        assert np.mean(got == ref) > 0.98
+        np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float64", "bfloat16"])
+@pytest.mark.parametrize("starting", [True, False])
+def test_sampled_triatt_elements_equal_the_full_restatement(starting, dtype):
+    rng = np.random.default_rng(32)
+    n = 36
+    params = orc.round_params(orc.random_triatt_params(rng, ln_noise=0.1, std=0.05), "bfloat16")
+    x = orc.round_bf16(rng.standard_normal((1, n, n, 128)).astype(np.float32))
+    mask = orc.pad_mask(n, 4)
+    full = orc.triangle_attention(params, x, mask, starting=starting, dtype=dtype)[0]
+    rows, cols = np.array([0, 9, 30]), np.array([2, 3, 19, 31])
+    xt, mt = (x[0], mask[0]) if starting else (x[0].transpose(1, 0, 2), mask[0].T)
+    got = orc.triangle_attention_sampled(params, xt[rows], mt[rows], xt[cols], cols, dtype=dtype)
+    ref = full[np.ix_(rows, cols)] if starting else full[np.ix_(cols, rows)].transpose(1, 0, 2)
+    if dtype == "float64":
+        np.testing.assert_allclose(got, ref, rtol=1e-9, atol=1e-11)
+    else:
+        assert np.mean(got == ref) > 0.97
+        np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-3)

@@ -285,3 +285,40 @@ def test_core_resumes_across_key_tiles(cuda_device):
         k0 += n_kt
     _lib.device_status()
     print(assert_parity(ref.float().cpu().numpy(), got.float().cpu().numpy(), label="resumed core", mean_tol=2e-4))
+
+
+def test_attention_core_scale_argument_and_mixed_mask_bias(cuda_device):
+    """The cuEquivariance calling convention (unscaled q plus ``scale``,
+    src/foldjax/models/_cueq.py:66-121) and an additive mask bias that mixes soft entries
+    with the -1e9 constant and -inf: the bias is added as given, not rebuilt from a 0/1 mask."""
+    from foldjax_b200.triangle_attention import attention_core
+    from foldjax_b200 import _lib
+
+    rng = np.random.default_rng(10)
+    lead, n_i, n_j, n_k, h, d = (2,), 7, 130, 90, 4, 32
+    shape = lambda n: lead + (n_i, h, n, d)
+    q = orc.round_bf16(rng.normal(size=shape(n_j), scale=2.5).astype(np.float32))
+    k = orc.round_bf16(rng.normal(size=shape(n_k), scale=0.5).astype(np.float32))
+    v = orc.round_bf16(rng.normal(size=shape(n_k)).astype(np.float32))
+    tb = orc.round_bf16(rng.normal(size=lead + (1, h, n_j, n_k), scale=2.0).astype(np.float32))
+    kind = rng.integers(0, 10, size=lead + (n_i, n_k))
+    mb = np.zeros(lead + (n_i, n_k), np.float32)
+    mb[kind == 0] = -1e9
+    mb[kind == 1] = -np.inf
+    soft = kind == 2
+    mb[soft] = -rng.random(soft.sum()).astype(np.float32) * 3.0  # soft biases beside the hard ones
+    mb[..., 0] = 0.0  # every row keeps at least one key
+    mb5 = mb[:, :, None, None, :]
+    scale = 1.0 / np.sqrt(d)
+    q_scaled = orc.round_bf16(q * orc.round_bf16(np.float32(scale)))
+    ref = orc.attention_core(q_scaled, k, v, tb, np.maximum(mb5, np.float32(-1e9)), dtype="bfloat16")
+    t = lambda a, dt: torch.from_numpy(a).to(cuda_device).to(dt)
+    got = attention_core(t(q, torch.bfloat16), t(k, torch.bfloat16), t(v, torch.bfloat16), t(tb, torch.bfloat16),
+                         t(mb5, torch.float32), scale=scale)
+    _lib.device_status()
+    assert got.shape == ref.shape and got.dtype == torch.bfloat16
+    print(assert_parity(ref, got.float().cpu().numpy(), label="attention_core scale= and mixed mask bias"))
+    # the soft entries matter: dropping them changes the result by far more than the tolerance
+    ref_nosoft = orc.attention_core(q_scaled, k, v, tb, np.where(soft[:, :, None, None, :], 0, np.maximum(mb5, -1e9)),
+                                    dtype="bfloat16")
+    assert orc.error_vs(ref_nosoft, got.float().cpu().numpy())["mean_abs_over_rms"] > 1e-2
