@@ -16,6 +16,7 @@ _HERE = Path(__file__).resolve().parent
 LIB_PATH = Path(os.environ.get("B200TRI_LIBRARY", _HERE / "libb200tri.so"))
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = range(6)
+DTYPE_BF16, DTYPE_F32 = 0, 1
 TRIATT_CORE_STATIC_MAX_FLOATS = 1 << 20
 
 
@@ -36,7 +37,7 @@ class TrimulArgs(C.Structure):
         ("norm_out_scale", C.c_void_p), ("norm_out_bias", C.c_void_p),
         ("p_out", C.c_void_p), ("g_out", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("dtype", C.c_int32),
     ]
 
 
@@ -89,7 +90,7 @@ class TriattArgs(C.Structure):
         ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p), ("w_bias", C.c_void_p),
         ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_g", C.c_void_p), ("w_o", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("dtype", C.c_int32),
     ]
 
 
@@ -150,6 +151,39 @@ class AttentionPairBiasArgs(C.Structure):
     ]
 
 
+class CpMsg(C.Structure):
+    _fields_ = [("src", C.c_int32), ("dst", C.c_int32), ("what", C.c_int32), ("block", C.c_int32),
+                ("slot0", C.c_int32), ("slot1", C.c_int32)]
+
+
+class TrimulCpArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("incoming", C.c_int32), ("eps", C.c_float),
+        ("x", C.c_void_p), ("mask", C.c_void_p),
+        ("norm_in_scale", C.c_void_p), ("norm_in_bias", C.c_void_p),
+        ("p_in", C.c_void_p), ("g_in", C.c_void_p),
+        ("norm_out_scale", C.c_void_p), ("norm_out_bias", C.c_void_p),
+        ("p_out", C.c_void_p), ("g_out", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class TriattCpArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("starting", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("inf", C.c_float), ("eps", C.c_float),
+        ("x", C.c_void_p), ("mask", C.c_void_p),
+        ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p), ("w_bias", C.c_void_p),
+        ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_g", C.c_void_p), ("w_o", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+COMM_ID_BYTES = 128
+CP_TRIMUL_OUTGOING, CP_TRIMUL_INCOMING, CP_TRIATT_STARTING, CP_TRIATT_ENDING = range(4)
+
 # C struct name -> ctypes mirror (tests compare sizeof on both sides)
 STRUCTS = {
     "b200tri_trimul_args": TrimulArgs,
@@ -162,6 +196,9 @@ STRUCTS = {
     "b200tri_triatt_finish_args": TriattFinishArgs,
     "b200tri_pair_transition_args": PairTransitionArgs,
     "b200tri_attention_pair_bias_args": AttentionPairBiasArgs,
+    "b200tri_cp_msg": CpMsg,
+    "b200tri_trimul_cp_args": TrimulCpArgs,
+    "b200tri_triatt_cp_args": TriattCpArgs,
 }
 
 # name -> (restype, argtypes); every symbol include/b200tri.h declares.
@@ -176,6 +213,8 @@ SIGNATURES = {
     "b200tri_timing_reset": (C.c_int, []),
     "b200tri_timing_read": (C.c_int, [C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_int32)]),
     "b200tri_trimul_workspace_bytes": (C.c_size_t, [C.c_int32]),
+    "b200tri_trimul_workspace_bytes_dtype": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "b200tri_triatt_workspace_bytes_dtype": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200tri_trimul_forward": (C.c_int, [C.POINTER(TrimulArgs), C.c_void_p]),
     "b200tri_trimul_project_workspace_bytes": (C.c_size_t, []),
     "b200tri_trimul_project": (C.c_int, [C.POINTER(TrimulProjectArgs), C.c_void_p]),
@@ -188,9 +227,25 @@ SIGNATURES = {
     "b200tri_triatt_project": (C.c_int, [C.POINTER(TriattProjectArgs), C.c_void_p]),
     "b200tri_triatt_core_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200tri_triatt_core": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
+    "b200tri_triatt_core_multi_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "b200tri_triatt_core_multi": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_int32, C.c_void_p]),
     "b200tri_triatt_core_static": (C.c_int, [C.POINTER(TriattCoreArgs), C.c_void_p]),
     "b200tri_triatt_finish_workspace_bytes": (C.c_size_t, []),
     "b200tri_triatt_finish": (C.c_int, [C.POINTER(TriattFinishArgs), C.c_void_p]),
+    "b200tri_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "b200tri_comm_init": (C.c_int, [C.POINTER(C.c_void_p), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "b200tri_comm_init_all": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32]),
+    "b200tri_comm_destroy": (C.c_int, [C.c_void_p]),
+    "b200tri_comm_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                    C.POINTER(C.c_int32)]),
+    "b200tri_comm_group_start": (C.c_int, []),
+    "b200tri_comm_group_end": (C.c_int, []),
+    "b200tri_comm_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200tri_cp_plan": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(CpMsg), C.c_int32]),
+    "b200tri_trimul_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),
+    "b200tri_trimul_cp": (C.c_int, [C.c_void_p, C.POINTER(TrimulCpArgs), C.c_void_p]),
+    "b200tri_triatt_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),
+    "b200tri_triatt_cp": (C.c_int, [C.c_void_p, C.POINTER(TriattCpArgs), C.c_void_p]),
     "b200tri_pair_transition_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_pair_transition": (C.c_int, [C.POINTER(PairTransitionArgs), C.c_void_p]),
     "b200tri_attention_pair_bias_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),

@@ -1,0 +1,774 @@
+// 2-D context parallelism behind the C ABI: a communicator over NCCL and the two
+// triangle ops on one rank's tile of the pair tensor.
+//
+// Reference: the 2-D layer of FoldJAX - context_parallel, src/foldjax/models/_cp.py:259;
+// _cannon_contract, src/foldjax/models/boltz2/models/triangle/triangle.py:132-212;
+// ring_triangle_attention_2d, src/foldjax/models/_cp_attention.py:197-403. The reference
+// runs inside shard_map on a square device grid and moves tiles with skews and ring hops;
+// here the grid is R x C with C = m * R (1x2, 2x2, 2x4 on one 8-GPU box) and every tile
+// is fetched straight from its owner with grouped ncclSend/ncclRecv: NVSwitch gives every
+// pair of GPUs the same bandwidth, so a rotated direct fetch replaces skew + hops.
+//
+// Everything is enqueue-only. The exchange runs on the communicator's own stream and is
+// fenced against the caller's stream with events in both directions, so the host never
+// waits; remote tiles always land in this GPU's memory before a kernel reads them (no
+// kernel is ever handed a peer pointer, and no TMA multicast exists anywhere).
+//
+// NCCL is reached through dlopen("libnccl.so.2") at the first communicator call: the
+// library itself has no link-time dependency on it and still loads where NCCL is absent.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "host.cuh"
+
+struct b200tri_comm {
+  ncclComm_t nccl = nullptr;
+  int world = 0, rank = 0, rows = 0, cols = 0, m = 0, r = 0, c = 0, device = 0;
+  cudaStream_t stream = nullptr;  // exchange stream
+  cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr;
+};
+
+namespace b200 {
+namespace {
+
+// ------------------------------------------------------------------ NCCL entry points
+struct Nccl {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+const Nccl* nccl_api() {
+  static Nccl api;
+  static bool tried = false;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (tried) return api.handle ? &api : nullptr;
+  tried = true;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return nullptr;
+  bool ok = true;
+  auto sym = [&](const char* name) {
+    void* p = dlsym(h, name);
+    ok = ok && p != nullptr;
+    return p;
+  };
+  api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+  api.CommInitAll = reinterpret_cast<decltype(api.CommInitAll)>(sym("ncclCommInitAll"));
+  api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+  api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+  api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+  api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+  api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+  api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+  if (!ok) return nullptr;
+  api.handle = h;
+  return &api;
+}
+
+#define B200_NCCL_OK(api, expr)                                                                         \
+  do {                                                                                                  \
+    ncclResult_t _r = (expr);                                                                           \
+    if (_r != ncclSuccess) {                                                                            \
+      b200::set_error("%s failed: %s (%s:%d)", #expr, (api)->GetErrorString(_r), __FILE__, __LINE__);   \
+      return B200TRI_ERR_CUDA;                                                                          \
+    }                                                                                                   \
+  } while (0)
+
+// ------------------------------------------------------------------------------ the plan
+// One message of an exchange: `what` names the sender's local array, `block` the row block
+// of it that travels (-1 = the whole tile), slot0/slot1 the position in the receiver's panel.
+enum { WHAT_A = 0, WHAT_B = 1, WHAT_KV = 2, WHAT_BIAS = 3 };
+using Msg = b200tri_cp_msg;
+
+struct Grid {
+  int rows, cols, m;
+  int rank(int r, int c) const { return r * cols + c; }
+};
+
+// The global message list of an op: the same on every rank, so that the sends of one rank
+// and the receives of its peer are posted in the same relative order.
+std::vector<Msg> build_plan(const Grid& g, int op) {
+  std::vector<Msg> msgs;
+  for (int dst = 0; dst < g.rows * g.cols; ++dst) {
+    const int r = dst / g.cols, c = dst % g.cols;
+    switch (op) {
+      case B200TRI_CP_TRIMUL_OUTGOING:
+        // out[I_r, J_c] = sum_c' a[I_r, K_c'] . b[J_c, K_c']^T: a tile of the row peer (r, c'),
+        // and the row block of b whose rows are J_c, which lives on (c / m, c').
+        for (int cp = 0; cp < g.cols; ++cp) {
+          msgs.push_back({g.rank(r, cp), dst, WHAT_A, -1, cp, 0});
+          msgs.push_back({g.rank(c / g.m, cp), dst, WHAT_B, c % g.m, cp, 0});
+        }
+        break;
+      case B200TRI_CP_TRIMUL_INCOMING:
+        // out[I_r, J_c] = sum_r'' a[K_r'', I_r]^T . b[K_r'', J_c], projected through swapped
+        // strides: output row block s needs a' of (r'', r * m + s); all need b' of (r'', c).
+        for (int rp = 0; rp < g.rows; ++rp) {
+          for (int s = 0; s < g.m; ++s) msgs.push_back({g.rank(rp, r * g.m + s), dst, WHAT_A, -1, s, rp});
+          msgs.push_back({g.rank(rp, c), dst, WHAT_B, -1, rp, 0});
+        }
+        break;
+      case B200TRI_CP_TRIATT_STARTING:
+        // rows I_r, queries J_c, keys of every K_c': K/V of (r, c'); the bias of (J_c, K_c') is
+        // row block c % m of the bias of (c / m, c').
+        for (int cp = 0; cp < g.cols; ++cp) {
+          msgs.push_back({g.rank(r, cp), dst, WHAT_KV, -1, cp, 0});
+          msgs.push_back({g.rank(c / g.m, cp), dst, WHAT_BIAS, c % g.m, cp, 0});
+        }
+        break;
+      case B200TRI_CP_TRIATT_ENDING:
+        // transposed frame: rows J_c, queries I_r, keys of every I_r'': K/V of (r'', c); the
+        // bias of (J_{r*m+s}, I_r'') is the whole bias of (r'', r * m + s).
+        for (int rp = 0; rp < g.rows; ++rp) {
+          msgs.push_back({g.rank(rp, c), dst, WHAT_KV, -1, rp, 0});
+          for (int s = 0; s < g.m; ++s) msgs.push_back({g.rank(rp, r * g.m + s), dst, WHAT_BIAS, -1, rp, s});
+        }
+        break;
+      default:
+        break;
+    }
+  }
+  return msgs;
+}
+
+struct Piece {
+  void* ptr;
+  size_t bytes;
+};
+
+// Byte offsets of 1 KiB-aligned pieces of a workspace.
+struct Offsets {
+  size_t off = 0;
+  size_t take(size_t bytes) {
+    off = (off + 1023) / 1024 * 1024;
+    const size_t r = off;
+    off += bytes;
+    return r;
+  }
+  size_t total() const { return (off + 1023) / 1024 * 1024; }
+};
+
+// Post this rank's share of `msgs` (those accepted by `want`): receives and sends as one NCCL
+// group on the exchange stream, local messages as device copies on the caller's stream.
+template <typename Want, typename Views>
+int post_exchange(b200tri_comm* cm, const std::vector<Msg>& msgs, Want want, Views views, cudaStream_t compute) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  std::vector<Piece> send, recv;
+  bool grouped = false;
+  for (const Msg& msg : msgs) {
+    if (!want(msg) || (msg.src != cm->rank && msg.dst != cm->rank)) continue;
+    send.clear();
+    recv.clear();
+    if (msg.src == cm->rank) views(msg, true, send);
+    if (msg.dst == cm->rank) views(msg, false, recv);
+    if (msg.src == cm->rank && msg.dst == cm->rank) {
+      for (size_t i = 0; i < send.size(); ++i)
+        if (send[i].ptr != recv[i].ptr)
+          B200_CUDA_OK(cudaMemcpyAsync(recv[i].ptr, send[i].ptr, send[i].bytes, cudaMemcpyDeviceToDevice, compute));
+      continue;
+    }
+    if (!grouped) {
+      B200_NCCL_OK(api, api->GroupStart());
+      grouped = true;
+    }
+    for (const Piece& p : send) B200_NCCL_OK(api, api->Send(p.ptr, p.bytes, ncclUint8, msg.dst, cm->nccl, cm->stream));
+    for (const Piece& p : recv) B200_NCCL_OK(api, api->Recv(p.ptr, p.bytes, ncclUint8, msg.src, cm->nccl, cm->stream));
+  }
+  if (grouped) B200_NCCL_OK(api, api->GroupEnd());
+  return B200TRI_OK;
+}
+
+int check_comm(const b200tri_comm* cm, const char* who) {
+  B200_REQUIRE(cm != nullptr && cm->nccl != nullptr, B200TRI_ERR_INVALID, "%s: null or destroyed communicator", who);
+  int dev = -1;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  B200_REQUIRE(dev == cm->device, B200TRI_ERR_INVALID, "%s: the communicator belongs to device %d, current device is %d",
+               who, cm->device, dev);
+  return B200TRI_OK;
+}
+
+int finish_init(b200tri_comm* cm, int world, int rank, int rows, int cols) {
+  cm->world = world;
+  cm->rank = rank;
+  cm->rows = rows;
+  cm->cols = cols;
+  cm->m = cols / rows;
+  cm->r = rank / cols;
+  cm->c = rank % cols;
+  B200_CUDA_OK(cudaGetDevice(&cm->device));
+  B200_CUDA_OK(cudaStreamCreateWithFlags(&cm->stream, cudaStreamNonBlocking));
+  B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_ready, cudaEventDisableTiming));
+  B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_first, cudaEventDisableTiming));
+  B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_rest, cudaEventDisableTiming));
+  return B200TRI_OK;
+}
+
+int check_grid(int world, int rows, int cols) {
+  B200_REQUIRE(rows >= 1 && cols >= 1 && rows * cols == world, B200TRI_ERR_INVALID,
+               "context-parallel grid %dx%d does not use %d ranks", rows, cols, world);
+  B200_REQUIRE(cols % rows == 0, B200TRI_ERR_UNSUPPORTED,
+               "unsupported context-parallel grid %dx%d: columns must be a multiple of rows", rows, cols);
+  return B200TRI_OK;
+}
+
+struct TileDims {
+  int n, n_r, n_c;
+};
+
+int tile_dims(const b200tri_comm* cm, int n, TileDims* d) {
+  B200_REQUIRE(n > 0 && n % cm->cols == 0, B200TRI_ERR_INVALID,
+               "token count %d is not divisible by the %d grid columns; pad it first", n, cm->cols);
+  d->n = n;
+  d->n_r = n / cm->rows;
+  d->n_c = n / cm->cols;
+  return B200TRI_OK;
+}
+
+// ---------------------------------------------------------------- tri-mult workspace
+struct TrimulPlan {
+  int n_outer, n_inner, n_src, n_k, ld, ldt, rpb, t_rpb;
+  size_t blk;  // elements of one n_c-row block of channel-major data [128][n_c][ld]
+  size_t a_all, a_loc, b_all, b_loc, t, proj, fin, total;  // byte offsets
+};
+
+TrimulPlan trimul_plan(const b200tri_comm* cm, const TileDims& d, bool incoming) {
+  TrimulPlan p;
+  const int R = cm->rows, C = cm->cols, m = cm->m;
+  p.n_outer = incoming ? d.n_c : d.n_r;
+  p.n_inner = incoming ? d.n_r : d.n_c;
+  p.n_src = incoming ? R : C;
+  p.n_k = p.n_inner;
+  p.ld = round_up(p.n_inner, 64);
+  p.ldt = round_up(d.n_c, 64);
+  p.rpb = d.n_c % 64 == 0 ? 64 : d.n_c;
+  p.t_rpb = p.rpb == 64 ? 64 : d.n_r;
+  p.blk = static_cast<size_t>(128) * d.n_c * p.ld;
+  Offsets w;
+  auto off = [&](size_t elems, size_t esize) { return w.take(elems * esize); };
+  if (!incoming) {
+    p.a_all = off(static_cast<size_t>(C) * m * p.blk, 2);  // slot c' <- a of (r, c')
+    p.b_loc = off(static_cast<size_t>(m) * p.blk, 2);
+    p.b_all = off(static_cast<size_t>(C) * p.blk, 2);      // slot c' <- block c % m of b of (c / m, c')
+    p.a_loc = p.a_all + static_cast<size_t>(cm->c) * m * p.blk * 2;
+  } else {
+    p.a_all = off(static_cast<size_t>(m) * R * p.blk, 2);  // slot (s, r'') <- a' of (r'', r * m + s)
+    p.a_loc = off(p.blk, 2);
+    p.b_all = off(static_cast<size_t>(R) * p.blk, 2);      // slot r'' <- b' of (r'', c)
+    p.b_loc = p.b_all + static_cast<size_t>(cm->r) * p.blk * 2;
+  }
+  p.t = off(static_cast<size_t>(128) * d.n_r * p.ldt, 2);
+  p.proj = off(b200tri_trimul_project_workspace_bytes(), 1);
+  p.fin = off(b200tri_trimul_finish_workspace_bytes(), 1);
+  p.total = w.total();
+  return p;
+}
+
+// ---------------------------------------------------------------- tri-attn workspace
+struct TriattPlan {
+  int n_outer, n_inner, n_q, tiles, own, ld;
+  size_t q, k_all, vt_all, bias_loc, bias_all, o, acc, rmax, rsum, proj, core, fin, total;
+  size_t k_tile, vt_tile, bias_tile;  // bytes of one key tile's K, V^T and bias
+};
+
+TriattPlan triatt_plan(const b200tri_comm* cm, const TileDims& d, bool starting) {
+  TriattPlan p;
+  p.n_outer = starting ? d.n_r : d.n_c;
+  p.n_inner = starting ? d.n_c : d.n_r;
+  p.n_q = p.n_inner;
+  p.tiles = starting ? cm->cols : cm->rows;
+  p.own = starting ? cm->c : cm->r;
+  p.ld = round_up(p.n_inner, 64);
+  p.k_tile = static_cast<size_t>(p.n_outer) * p.n_inner * 128 * 2;
+  p.vt_tile = static_cast<size_t>(p.n_outer) * 128 * p.ld * 2;
+  p.bias_tile = static_cast<size_t>(4) * p.n_q * p.ld * 2;
+  Offsets w;
+  auto off = [&](size_t bytes) { return w.take(bytes); };
+  p.q = off(p.k_tile);
+  p.k_all = off(p.k_tile * p.tiles);
+  p.vt_all = off(p.vt_tile * p.tiles);
+  p.bias_loc = off(static_cast<size_t>(4) * p.n_outer * p.ld * 2);
+  p.bias_all = off(p.bias_tile * p.tiles);
+  p.o = off(static_cast<size_t>(p.n_outer) * p.n_q * 128 * 2);
+  p.acc = off(static_cast<size_t>(p.n_outer) * p.n_q * 128 * 4);
+  p.rmax = off(static_cast<size_t>(p.n_outer) * 4 * p.n_q * 4);
+  p.rsum = off(static_cast<size_t>(p.n_outer) * 4 * p.n_q * 4);
+  p.proj = off(b200tri_triatt_project_workspace_bytes());
+  p.core = off(b200tri_triatt_core_multi_workspace_bytes(p.n_outer, p.n_inner, p.tiles));
+  p.fin = off(b200tri_triatt_finish_workspace_bytes());
+  p.total = w.total();
+  return p;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+// ============================================================================ C ABI
+extern "C" int b200tri_cp_plan(int32_t rows, int32_t cols, int32_t op, b200tri_cp_msg* out, int32_t capacity) {
+  if (check_grid(rows * cols, rows, cols)) return -1;
+  if (op < B200TRI_CP_TRIMUL_OUTGOING || op > B200TRI_CP_TRIATT_ENDING) {
+    set_error("cp_plan: unknown op %d", op);
+    return -1;
+  }
+  const std::vector<Msg> msgs = build_plan(Grid{rows, cols, cols / rows}, op);
+  if (out)
+    for (size_t i = 0; i < msgs.size() && static_cast<int32_t>(i) < capacity; ++i) out[i] = msgs[i];
+  return static_cast<int>(msgs.size());
+}
+
+extern "C" int b200tri_comm_unique_id(void* id128) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  B200_REQUIRE(id128 != nullptr, B200TRI_ERR_INVALID, "comm_unique_id: null buffer");
+  static_assert(sizeof(ncclUniqueId) == B200TRI_COMM_ID_BYTES, "NCCL unique id size");
+  B200_NCCL_OK(api, api->GetUniqueId(static_cast<ncclUniqueId*>(id128)));
+  return B200TRI_OK;
+}
+
+extern "C" int b200tri_comm_init(b200tri_comm** out, const void* id128, int32_t world, int32_t rank, int32_t rows,
+                                 int32_t cols) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  B200_REQUIRE(out && id128, B200TRI_ERR_INVALID, "comm_init: null argument");
+  B200_REQUIRE(rank >= 0 && rank < world, B200TRI_ERR_INVALID, "comm_init: rank %d outside [0, %d)", rank, world);
+  int rc = check_grid(world, rows, cols);
+  if (rc) return rc;
+  b200tri_comm* cm = new b200tri_comm;
+  ncclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  ncclResult_t r = api->CommInitRank(&cm->nccl, world, id, rank);
+  if (r != ncclSuccess) {
+    set_error("ncclCommInitRank failed: %s", api->GetErrorString(r));
+    delete cm;
+    return B200TRI_ERR_CUDA;
+  }
+  rc = finish_init(cm, world, rank, rows, cols);
+  if (rc) {
+    b200tri_comm_destroy(cm);
+    return rc;
+  }
+  *out = cm;
+  return B200TRI_OK;
+}
+
+extern "C" int b200tri_comm_init_all(b200tri_comm** out, const int32_t* devices, int32_t world, int32_t rows,
+                                     int32_t cols) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  B200_REQUIRE(out && world >= 1 && world <= 64, B200TRI_ERR_INVALID, "comm_init_all: bad arguments");
+  int rc = check_grid(world, rows, cols);
+  if (rc) return rc;
+  std::vector<ncclComm_t> comms(world);
+  std::vector<int> devs(world);
+  for (int i = 0; i < world; ++i) devs[i] = devices ? devices[i] : i;
+  B200_NCCL_OK(api, api->CommInitAll(comms.data(), world, devs.data()));
+  int prev = 0;
+  B200_CUDA_OK(cudaGetDevice(&prev));
+  for (int i = 0; i < world; ++i) {
+    out[i] = new b200tri_comm;
+    out[i]->nccl = comms[i];
+    B200_CUDA_OK(cudaSetDevice(devs[i]));
+    rc = finish_init(out[i], world, i, rows, cols);
+    if (rc) break;
+  }
+  cudaSetDevice(prev);
+  return rc;
+}
+
+extern "C" int b200tri_comm_destroy(b200tri_comm* cm) {
+  if (!cm) return B200TRI_OK;
+  const Nccl* api = nccl_api();
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(cm->device);
+  if (cm->stream) cudaStreamSynchronize(cm->stream);
+  if (cm->nccl && api) api->CommDestroy(cm->nccl);
+  if (cm->ev_ready) cudaEventDestroy(cm->ev_ready);
+  if (cm->ev_first) cudaEventDestroy(cm->ev_first);
+  if (cm->ev_rest) cudaEventDestroy(cm->ev_rest);
+  if (cm->stream) cudaStreamDestroy(cm->stream);
+  cudaSetDevice(prev);
+  delete cm;
+  return B200TRI_OK;
+}
+
+extern "C" int b200tri_comm_info(const b200tri_comm* cm, int32_t* world, int32_t* rank, int32_t* rows, int32_t* cols) {
+  B200_REQUIRE(cm != nullptr, B200TRI_ERR_INVALID, "comm_info: null communicator");
+  if (world) *world = cm->world;
+  if (rank) *rank = cm->rank;
+  if (rows) *rows = cm->rows;
+  if (cols) *cols = cm->cols;
+  return B200TRI_OK;
+}
+
+extern "C" int b200tri_comm_group_start(void) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  B200_NCCL_OK(api, api->GroupStart());
+  return B200TRI_OK;
+}
+
+extern "C" int b200tri_comm_group_end(void) {
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  B200_NCCL_OK(api, api->GroupEnd());
+  return B200TRI_OK;
+}
+
+// Every rank sends `bytes` from `shard` to every other rank and receives theirs into
+// gathered[src * bytes ...] (its own shard is copied): an all-gather through the very
+// send/receive path the ops use. The host compares the result with what was sent.
+extern "C" int b200tri_comm_probe(b200tri_comm* cm, const void* shard, void* gathered, size_t bytes,
+                                  b200tri_stream_t stream_) {
+  int rc = check_comm(cm, "comm_probe");
+  if (rc) return rc;
+  B200_REQUIRE(shard && gathered && bytes > 0, B200TRI_ERR_INVALID, "comm_probe: null buffer or zero size");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  std::vector<Msg> msgs;
+  for (int dst = 0; dst < cm->world; ++dst)
+    for (int src = 0; src < cm->world; ++src) msgs.push_back({src, dst, WHAT_A, -1, src, 0});
+  B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  rc = post_exchange(
+      cm, msgs, [](const Msg&) { return true; },
+      [&](const Msg& msg, bool send, std::vector<Piece>& out) {
+        if (send)
+          out.push_back({const_cast<void*>(shard), bytes});
+        else
+          out.push_back({static_cast<uint8_t*>(gathered) + static_cast<size_t>(msg.slot0) * bytes, bytes});
+      },
+      stream);
+  if (rc) return rc;
+  B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+  return B200TRI_OK;
+}
+
+// ---------------------------------------------------------------------------- tri-mult
+extern "C" size_t b200tri_trimul_cp_workspace_bytes(const b200tri_comm* cm, int32_t n) {
+  if (!cm || n <= 0 || n % cm->cols) return 0;
+  TileDims d;
+  if (tile_dims(cm, n, &d)) return 0;
+  const size_t a = trimul_plan(cm, d, false).total, b = trimul_plan(cm, d, true).total;
+  return (a > b ? a : b) + 1024;
+}
+
+extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args* a, b200tri_stream_t stream_) {
+  int rc = check_comm(cm, "trimul_cp");
+  if (rc) return rc;
+  B200_REQUIRE(a != nullptr && a->x && a->out, B200TRI_ERR_INVALID, "trimul_cp: null args, x or out");
+  TileDims d;
+  if ((rc = tile_dims(cm, a->n, &d))) return rc;
+  const bool incoming = a->incoming != 0;
+  const TrimulPlan pl = trimul_plan(cm, d, incoming);
+  B200_REQUIRE(a->workspace && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,
+               "trimul_cp: workspace of %zu bytes needed, got %zu", pl.total, a->workspace_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
+               "trimul_cp: workspace must be 1024-byte aligned");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const int R = cm->rows, C = cm->cols, m = cm->m, r = cm->r, c = cm->c;
+  const int64_t n = d.n, n_r = d.n_r, n_c = d.n_c;
+  (void)R;
+  (void)C;
+
+  // local projection of this rank's tile
+  b200tri_trimul_project_args pa = {};
+  pa.n_outer = pl.n_outer;
+  pa.n_inner = pl.n_inner;
+  pa.eps = a->eps;
+  pa.x = a->x;
+  pa.xs_outer = incoming ? 128 : n_c * 128;
+  pa.xs_inner = incoming ? n_c * 128 : 128;
+  if (a->mask) {
+    pa.mask = a->mask + (static_cast<int64_t>(r) * n_r * n + static_cast<int64_t>(c) * n_c);
+    pa.ms_outer = incoming ? 1 : n;
+    pa.ms_inner = incoming ? n : 1;
+  }
+  pa.norm_in_scale = a->norm_in_scale;
+  pa.norm_in_bias = a->norm_in_bias;
+  pa.p_in = a->p_in;
+  pa.g_in = a->g_in;
+  pa.a = ws + pl.a_loc;
+  pa.b = ws + pl.b_loc;
+  pa.ld = pl.ld;
+  pa.chan_stride = static_cast<int64_t>(pl.rpb) * pl.ld;
+  pa.block_stride = static_cast<int64_t>(128) * pl.rpb * pl.ld;
+  pa.rows_per_block = pl.rpb;
+  pa.workspace = ws + pl.proj;
+  pa.workspace_bytes = b200tri_trimul_project_workspace_bytes();
+  if ((rc = b200tri_trimul_project(&pa, stream_))) return rc;
+
+  // exchange: ordered after the projection, the contraction ordered after it
+  const size_t blk_bytes = pl.blk * 2;
+  B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  const std::vector<Msg> msgs =
+      build_plan(Grid{cm->rows, cm->cols, m}, incoming ? B200TRI_CP_TRIMUL_INCOMING : B200TRI_CP_TRIMUL_OUTGOING);
+  rc = post_exchange(
+      cm, msgs, [](const Msg&) { return true; },
+      [&](const Msg& msg, bool send, std::vector<Piece>& out) {
+        if (send) {
+          uint8_t* src = ws + (msg.what == WHAT_A ? pl.a_loc : pl.b_loc);
+          if (msg.block < 0) {  // a whole local array: m blocks (outgoing a), or one block
+            const size_t whole = (!incoming && msg.what == WHAT_A) ? blk_bytes * m : blk_bytes;
+            out.push_back({src, whole});
+          } else {
+            out.push_back({src + blk_bytes * msg.block, blk_bytes});
+          }
+          return;
+        }
+        if (!incoming) {
+          if (msg.what == WHAT_A)
+            out.push_back({ws + pl.a_all + blk_bytes * m * msg.slot0, blk_bytes * m});
+          else
+            out.push_back({ws + pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+        } else {
+          if (msg.what == WHAT_A)
+            out.push_back({ws + pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1), blk_bytes});
+          else
+            out.push_back({ws + pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+        }
+      },
+      stream);
+  if (rc) return rc;
+  B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+
+  // one contraction launch per output row block walks all k-sources (fp32 accumulation on chip)
+  const int64_t t_chan = static_cast<int64_t>(pl.t_rpb) * pl.ldt;
+  const int64_t t_row = pl.rpb == 64 ? static_cast<int64_t>(128) * pl.ldt : pl.ldt;
+  for (int s = 0; s < m; ++s) {
+    b200tri_trimul_contract_args ca = {};
+    ca.n_i = ca.n_j = static_cast<int32_t>(n_c);
+    ca.n_k = pl.n_k;
+    ca.n_src = pl.n_src;
+    if (!incoming) {
+      ca.a = ws + pl.a_all + blk_bytes * s;
+      ca.a_src_stride = static_cast<int64_t>(pl.blk) * m;
+    } else {
+      ca.a = ws + pl.a_all + blk_bytes * (static_cast<size_t>(s) * cm->rows);
+      ca.a_src_stride = static_cast<int64_t>(pl.blk);
+    }
+    ca.b = ws + pl.b_all;
+    ca.b_src_stride = static_cast<int64_t>(pl.blk);
+    ca.a_ld = ca.b_ld = pl.ld;
+    ca.a_chan_stride = ca.b_chan_stride = static_cast<int64_t>(pl.rpb) * pl.ld;
+    ca.out_bf16 = ws + pl.t + static_cast<size_t>(2) * s * n_c * t_row;
+    ca.out_ld = pl.ldt;
+    ca.out_chan_stride = t_chan;
+    ca.a_rows_per_block = ca.b_rows_per_block = pl.rpb;
+    ca.out_rows_per_block = pl.t_rpb;
+    ca.a_block_stride = ca.b_block_stride = static_cast<int64_t>(128) * pl.rpb * pl.ld;
+    ca.out_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
+    if ((rc = b200tri_trimul_contract(&ca, stream_))) return rc;
+  }
+
+  b200tri_trimul_finish_args fa = {};
+  fa.n_i = static_cast<int32_t>(n_r);
+  fa.n_j = static_cast<int32_t>(n_c);
+  fa.eps = a->eps;
+  fa.t = ws + pl.t;
+  fa.t_ld = pl.ldt;
+  fa.t_chan_stride = t_chan;
+  fa.t_rows_per_block = pl.t_rpb;
+  fa.t_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
+  fa.x = a->x;
+  fa.xs_i = n_c * 128;
+  fa.xs_j = 128;
+  fa.norm_in_scale = a->norm_in_scale;
+  fa.norm_in_bias = a->norm_in_bias;
+  fa.norm_out_scale = a->norm_out_scale;
+  fa.norm_out_bias = a->norm_out_bias;
+  fa.p_out = a->p_out;
+  fa.g_out = a->g_out;
+  fa.residual = a->residual;
+  fa.out = a->out;
+  fa.os_i = n_c * 128;
+  fa.os_j = 128;
+  fa.workspace = ws + pl.fin;
+  fa.workspace_bytes = b200tri_trimul_finish_workspace_bytes();
+  return b200tri_trimul_finish(&fa, stream_);
+}
+
+// ---------------------------------------------------------------------------- tri-attn
+extern "C" size_t b200tri_triatt_cp_workspace_bytes(const b200tri_comm* cm, int32_t n) {
+  if (!cm || n <= 0 || n % cm->cols) return 0;
+  TileDims d;
+  if (tile_dims(cm, n, &d)) return 0;
+  const size_t a = triatt_plan(cm, d, true).total, b = triatt_plan(cm, d, false).total;
+  return (a > b ? a : b) + 1024;
+}
+
+extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args* a, b200tri_stream_t stream_) {
+  int rc = check_comm(cm, "triatt_cp");
+  if (rc) return rc;
+  B200_REQUIRE(a != nullptr && a->x && a->out, B200TRI_ERR_INVALID, "triatt_cp: null args, x or out");
+  B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
+               "triatt_cp: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
+  TileDims d;
+  if ((rc = tile_dims(cm, a->n, &d))) return rc;
+  const bool starting = a->starting != 0;
+  const TriattPlan pl = triatt_plan(cm, d, starting);
+  B200_REQUIRE(pl.tiles <= 1 + 7, B200TRI_ERR_UNSUPPORTED, "triatt_cp: at most 8 key tiles per ring (got %d)", pl.tiles);
+  B200_REQUIRE(a->workspace && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,
+               "triatt_cp: workspace of %zu bytes needed, got %zu", pl.total, a->workspace_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
+               "triatt_cp: workspace must be 1024-byte aligned");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const int m = cm->m, r = cm->r, c = cm->c;
+  const int64_t n = d.n, n_r = d.n_r, n_c = d.n_c;
+  const int64_t xs_o = starting ? n_c * 128 : 128, xs_i = starting ? 128 : n_c * 128;
+
+  b200tri_triatt_project_args pa = {};
+  pa.n_outer = pl.n_outer;
+  pa.n_inner = pl.n_inner;
+  pa.heads = a->heads;
+  pa.head_dim = a->head_dim;
+  pa.eps = a->eps;
+  pa.x = a->x;
+  pa.xs_outer = xs_o;
+  pa.xs_inner = xs_i;
+  pa.norm_scale = a->norm_scale;
+  pa.norm_bias = a->norm_bias;
+  pa.w_q = a->w_q;
+  pa.w_k = a->w_k;
+  pa.w_v = a->w_v;
+  pa.w_bias = a->w_bias;
+  pa.q = ws + pl.q;
+  pa.k = ws + pl.k_all + pl.k_tile * pl.own;
+  pa.vt = ws + pl.vt_all + pl.vt_tile * pl.own;
+  pa.bias = ws + pl.bias_loc;
+  pa.ld = pl.ld;
+  pa.bias_head_stride = static_cast<int64_t>(pl.n_outer) * pl.ld;
+  pa.workspace = ws + pl.proj;
+  pa.workspace_bytes = b200tri_triatt_project_workspace_bytes();
+  if ((rc = b200tri_triatt_project(&pa, stream_))) return rc;
+
+  // Two groups on the exchange stream: the bias chunks (small; even the own key tile's bias
+  // may live on another rank) fence the first core launch, the peers' K/V tiles only the
+  // second one, so they travel while the own key tile is computed.
+  B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  const std::vector<Msg> msgs =
+      build_plan(Grid{cm->rows, cm->cols, m}, starting ? B200TRI_CP_TRIATT_STARTING : B200TRI_CP_TRIATT_ENDING);
+  const size_t head_rows = static_cast<size_t>(pl.n_outer) * pl.ld * 2;  // one head of the sender's bias
+  const size_t qhead = static_cast<size_t>(pl.n_q) * pl.ld * 2;          // one head of a received bias tile
+  const size_t chunk = static_cast<size_t>(n_c) * pl.ld * 2;             // n_c bias rows
+  auto views = [&](const Msg& msg, bool send, std::vector<Piece>& out) {
+    if (msg.what == WHAT_KV) {
+      const int slot = send ? pl.own : msg.slot0;
+      out.push_back({ws + pl.k_all + pl.k_tile * slot, pl.k_tile});
+      out.push_back({ws + pl.vt_all + pl.vt_tile * slot, pl.vt_tile});
+      return;
+    }
+    for (int h = 0; h < 4; ++h) {
+      if (starting) {  // row block of the sender's bias -> the whole bias of one key tile
+        if (send)
+          out.push_back({ws + pl.bias_loc + head_rows * h + chunk * msg.block, chunk});
+        else
+          out.push_back({ws + pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h, chunk});
+      } else {  // the sender's whole bias -> one query block of one key tile
+        if (send)
+          out.push_back({ws + pl.bias_loc + head_rows * h, chunk});
+        else
+          out.push_back({ws + pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h + chunk * msg.slot1, chunk});
+      }
+    }
+  };
+  if ((rc = post_exchange(cm, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
+  B200_CUDA_OK(cudaEventRecord(cm->ev_first, cm->stream));
+  if ((rc = post_exchange(cm, msgs, [](const Msg& x) { return x.what == WHAT_KV; }, views, stream))) return rc;
+  B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
+
+  // key tiles: the own one first, then the peers' in rotated order (every sender serves a
+  // different receiver at each position), all of them in one resumed launch
+  b200tri_triatt_core_args tiles[8] = {};
+  for (int idx = 0; idx < pl.tiles; ++idx) {
+    const int t = (pl.own + idx) % pl.tiles;
+    b200tri_triatt_core_args& ca = tiles[idx];
+    ca.n_i = pl.n_outer;
+    ca.n_j = pl.n_q;
+    ca.n_k = pl.n_inner;
+    ca.heads = a->heads;
+    ca.head_dim = a->head_dim;
+    ca.q = ws + pl.q;
+    ca.k = ws + pl.k_all + pl.k_tile * t;
+    ca.vt = ws + pl.vt_all + pl.vt_tile * t;
+    ca.v_ld = pl.ld;
+    ca.bias = ws + pl.bias_all + pl.bias_tile * t;
+    ca.bias_ld = pl.ld;
+    ca.bias_head_stride = static_cast<int64_t>(pl.n_q) * pl.ld;
+    if (a->mask) {
+      if (starting) {  // rows I_r, keys K_t
+        ca.mask = a->mask + (static_cast<int64_t>(r) * n_r * n + static_cast<int64_t>(t) * n_c);
+        ca.ms_i = n;
+        ca.ms_k = 1;
+      } else {  // rows J_c, keys I_t of the transposed mask
+        ca.mask = a->mask + (static_cast<int64_t>(t) * n_r * n + static_cast<int64_t>(c) * n_c);
+        ca.ms_i = 1;
+        ca.ms_k = n;
+      }
+    }
+    ca.inf = a->inf;
+    ca.o = ws + pl.o;
+    ca.row_max = reinterpret_cast<float*>(ws + pl.rmax);
+    ca.row_sum = reinterpret_cast<float*>(ws + pl.rsum);
+    ca.acc_o = reinterpret_cast<float*>(ws + pl.acc);
+    ca.workspace = ws + pl.core;
+    ca.workspace_bytes = b200tri_triatt_core_multi_workspace_bytes(pl.n_outer, pl.n_inner, pl.tiles);
+  }
+  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_first, 0));
+  tiles[0].unnormalized = pl.tiles > 1;
+  if ((rc = b200tri_triatt_core(&tiles[0], stream_))) return rc;
+  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+  if (pl.tiles > 1) {
+    if (pl.n_inner % 64 == 0) {
+      tiles[1].resume = 1;
+      if ((rc = b200tri_triatt_core_multi(&tiles[1], pl.tiles - 1, stream_))) return rc;
+    } else {  // ragged key tiles: one launch each, the state carried in acc_o
+      for (int idx = 1; idx < pl.tiles; ++idx) {
+        tiles[idx].resume = 1;
+        tiles[idx].unnormalized = idx + 1 < pl.tiles;
+        if ((rc = b200tri_triatt_core(&tiles[idx], stream_))) return rc;
+      }
+    }
+  }
+
+  b200tri_triatt_finish_args fa = {};
+  fa.n_outer = pl.n_outer;
+  fa.n_inner = pl.n_inner;
+  fa.eps = a->eps;
+  fa.o = ws + pl.o;
+  fa.x = a->x;
+  fa.xs_outer = xs_o;
+  fa.xs_inner = xs_i;
+  fa.norm_scale = a->norm_scale;
+  fa.norm_bias = a->norm_bias;
+  fa.w_g = a->w_g;
+  fa.w_o = a->w_o;
+  fa.residual = a->residual;
+  fa.out = a->out;
+  fa.os_outer = xs_o;
+  fa.os_inner = xs_i;
+  fa.workspace = ws + pl.fin;
+  fa.workspace_bytes = b200tri_triatt_finish_workspace_bytes();
+  return b200tri_triatt_finish(&fa, stream_);
+}

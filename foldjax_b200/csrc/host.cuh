@@ -71,6 +71,12 @@ int sm_count();
 // from several host threads (one per device under XLA).
 int ensure_smem_limit(const void* kernel, int bytes);
 
+// float32 mode of the two module-level entries (fp32_mode.cu).
+size_t trimul_workspace_bytes_f32(int32_t n);
+size_t triatt_workspace_bytes_f32(int32_t n);
+int trimul_forward_f32(const b200tri_trimul_args* a, cudaStream_t stream);
+int triatt_forward_f32(const b200tri_triatt_args* a, cudaStream_t stream);
+
 // Launch accounting and optional per-kernel event timing.
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
                 K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_COUNT };

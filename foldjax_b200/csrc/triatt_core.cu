@@ -44,22 +44,20 @@ namespace {
 #define B200_NWG 3
 #endif
 #ifndef B200_TURNS
-#define B200_TURNS 1
+#define B200_TURNS 0
 #endif
 // 1: the pair bias is added by the tensor core (S = bias . I + Q . K^T); 0: by the softmax threads.
 #ifndef B200_BIAS_MMA
 #define B200_BIAS_MMA 1
 #endif
-// 1: the exponentials of a step start from the offset of the previous steps while the
-// step's maximum is still being reduced; they are redone when the offset has to move.
-#ifndef B200_SPEC
-#define B200_SPEC 1
-#endif
 // Of every 16 pairs of exponentials, this many are evaluated on the FMA pipe.
 #ifndef B200_POLY
-#define B200_POLY 0
+#define B200_POLY 8
 #endif
 // 1: registers are moved from the control warpgroup to the softmax warpgroups at start-up.
+#ifndef B200_POLY_IMAD
+#define B200_POLY_IMAD 0
+#endif
 #ifndef B200_SETMAXNREG
 #define B200_SETMAXNREG 1
 #endif
@@ -75,7 +73,9 @@ constexpr int V_BYTES = V_ROWS * 128;  // [48][64 k] fp16; TMA fills rows 0..31
 constexpr int V_TMA_BYTES = 32 * 128;
 constexpr uint32_t TM_S = 0, TM_P = 64, TM_O = 96, TM_L = 128, TM_WG = 160;  // O: 32 columns + the row sum in column 128
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr float RESCALE_THRESHOLD = 5.5f;  // natural-log units, about 8 in log2
+constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: P stays below 2^8.5
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float EXP_MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
 // A dropped key's score. The reference adds -1e9 in fp32, which absorbs q.k + bias
 // (|q.k + bias| < 32 is below half an ulp of 1e9): every dropped key ends up with
 // the same score, so a row with no valid key becomes a uniform average. Here a
@@ -101,8 +101,16 @@ struct Smem {
 static_assert(sizeof(Smem) <= 232448, "shared memory budget");
 constexpr uint32_t STAGE_TX = BIAS_BYTES + NWG * (K_BYTES + V_TMA_BYTES + KT * 4);
 
+// One launch can walk several key tiles (ring attention: the tiles of the peers, each in
+// its own buffers): per tile one tensor map for K, V^T, the pair bias and the mask-bias rows.
+constexpr int MAX_KEY_TILES = 7;
+struct TileMaps {
+  CUtensorMap k[MAX_KEY_TILES], v[MAX_KEY_TILES], b[MAX_KEY_TILES], m[MAX_KEY_TILES];
+};
+
 struct Params {
-  int n_i, n_j, n_k;  // rows, queries, keys
+  int n_i, n_j, n_k;  // rows, queries, keys per key tile
+  int steps_per_tile;
   int heads;
   int groups, tiles_j, steps;
   long long total_items;
@@ -122,26 +130,34 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
   return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-// 2^t for a pair on the FMA pipe: t = n + f with n the nearest integer (taken from the low
-// mantissa bits after adding 1.5 * 2^23) and |f| <= 0.5; a cubic for 2^f (2e-4 relative, below
-// the fp16 rounding P gets anyway); n goes straight into the exponent field. Inputs below -120
-// (masked and padded keys) are clamped and round to zero as fp16.
-__device__ __forceinline__ float2 poly_exp2x2(float2 t) {
-  const float2 magic = make_float2(12582912.0f, 12582912.0f);
-  t = make_float2(fmaxf(t.x, -120.0f), fmaxf(t.y, -120.0f));
-  const float2 y = __fadd2_rn(t, magic);
-  const float2 f = __fadd2_rn(t, __fadd2_rn(magic, make_float2(-y.x, -y.y)));
+// 2^(u * log2e - m2) for a pair of scores on the FMA pipe instead of the MUFU unit, m2 an
+// integer: y = u * log2e + (magic - m2) holds n = round(t) in its low mantissa bits,
+// f = u * log2e - m2 - n is formed with one more fma (|f| <= 0.5), a cubic gives 2^f to
+// 2e-4 relative (below the fp16 rounding P gets anyway) and n is added to the exponent
+// field. `u` must have been clamped so that t >= -125 (the caller does it): the exponent
+// arithmetic has no underflow handling.
+__device__ __forceinline__ float2 poly_exp2x2(float2 u, float2 log2e2, float2 magic_minus_m2) {
+  const float2 y = __ffma2_rn(u, log2e2, magic_minus_m2);
+  const float2 d = __ffma2_rn(y, make_float2(-1.0f, -1.0f), magic_minus_m2);  // -(m2 + n), exact
+  const float2 f = __ffma2_rn(u, log2e2, d);
   float2 q = __ffma2_rn(make_float2(0.05286743f, 0.05286743f), f, make_float2(0.24215189f, 0.24215189f));
   q = __ffma2_rn(q, f, make_float2(0.69358677f, 0.69358677f));
   q = __ffma2_rn(q, f, make_float2(0.99996275f, 0.99996275f));
+#if B200_POLY_IMAD
+  // bits(q) + (bits(y) << 23) as one integer multiply-add per value (FMA pipe) instead of a
+  // shift and an add on the ALU pipe, which the maxima and clamps already load.
+  int rx, ry;
+  asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(rx) : "r"(__float_as_int(y.x)), "r"(__float_as_int(q.x)));
+  asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(ry) : "r"(__float_as_int(y.y)), "r"(__float_as_int(q.y)));
+  return make_float2(__int_as_float(rx), __int_as_float(ry));
+#else
   return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(y.x) << 23)),
                      __int_as_float(__float_as_int(q.y) + (__float_as_int(y.y) << 23)));
+#endif
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                const __grid_constant__ CUtensorMap tm_m, const Params p) {
+att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ TileMaps tm, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
@@ -152,10 +168,10 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-    tma_prefetch_desc(&tm_b);
-    tma_prefetch_desc(&tm_m);
+    tma_prefetch_desc(&tm.k[0]);
+    tma_prefetch_desc(&tm.v[0]);
+    tma_prefetch_desc(&tm.b[0]);
+    tma_prefetch_desc(&tm.m[0]);
     mbar_init(&sm.q_full, 1);
     mbar_init(&sm.q_empty, 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -231,13 +247,14 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             alive = false;
             break;
           }
-          const int k0 = t * KT;
+          const int tile = t / p.steps_per_tile;
+          const int k0 = (t - tile * p.steps_per_tile) * KT;
           mbar_expect_tx(&sm.st_full[stage], STAGE_TX);
-          tma_load_3d(sm.bias[stage], &tm_b, &sm.st_full[stage], k0, j0, h);
+          tma_load_3d(sm.bias[stage], &tm.b[tile], &sm.st_full[stage], k0, j0, h);
           for (int g = 0; g < NWG; ++g) {
-            tma_load_3d(sm.k[stage][g], &tm_k, &sm.st_full[stage], h * 32, k0, i0 + g);
-            tma_load_3d(sm.v[stage][g], &tm_v, &sm.st_full[stage], k0, h * 32, i0 + g);
-            tma_load_2d(sm.mb[stage][g], &tm_m, &sm.st_full[stage], k0, i0 + g);
+            tma_load_3d(sm.k[stage][g], &tm.k[tile], &sm.st_full[stage], h * 32, k0, i0 + g);
+            tma_load_3d(sm.v[stage][g], &tm.v[tile], &sm.st_full[stage], k0, h * 32, i0 + g);
+            tma_load_2d(sm.mb[stage][g], &tm.m[tile], &sm.st_full[stage], k0, i0 + g);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -349,7 +366,10 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int rem = static_cast<int>(item % items_per_head);
       const int i = (rem / p.tiles_j) * NWG + wg;
       const int j = (rem % p.tiles_j) * 128 + row;
-      float m_run = -INFINITY, m_used = -INFINITY;
+      // The softmax offset, kept in log2 units and integer-valued: exp(s - m) is evaluated as
+      // 2^(s * log2e - m2). An integer m2 lets the polynomial path fold it into its range
+      // reduction exactly and makes every rescale factor an exact power of two.
+      float m2_used = -INFINITY;
       const bool in_range = i < p.n_i && j < p.n_j;
       const long long si = (static_cast<long long>(i) * p.heads + h) * p.n_j + j;
       const long long oi = (static_cast<long long>(i) * p.n_j + j) * 128 + h * 32;
@@ -364,7 +384,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[e] = 0u;
         if (in_range) {
-          m_used = p.row_max[si];
+          m2_used = rintf(p.row_max[si] * LOG2E);
           lcol[0] = __float_as_uint(p.row_sum[si]);
           const float4* src = reinterpret_cast<const float4*>(p.acc_o + oi);
 #pragma unroll
@@ -376,7 +396,6 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             o[4 * q4 + 3] = __float_as_uint(f.w);
           }
         }
-        m_run = m_used;
         tmem_st32(t_wg + TM_O, o);
         tmem_st16(t_wg + TM_L, lcol);
         tmem_st_wait();
@@ -475,44 +494,6 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
 #endif
-        // exp(u - m) = exp2(u * log2e - m * log2e), one fma per pair (|m| <= 3e4, so the
-        // product m * log2e is good to 0.002 in the exponent, and exact cancellation
-        // for the keys that equal the offset).
-        // P goes to TMEM in two halves of 32 keys to keep the live registers down.
-        const float2 log2e2 = make_float2(LOG2E, LOG2E);
-        auto emit_p = [&](float offset) {
-          const float nm = -offset * LOG2E;
-          const float2 nm2 = make_float2(nm, nm);
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const float2 ue = u[16 * half + e];
-              const float2 t2 = __ffma2_rn(ue, log2e2, nm2);
-              float2 ex;
-              if (e >= 16 - B200_POLY) {
-                ex = poly_exp2x2(t2);
-              } else {
-                ex = make_float2(fast_exp2(t2.x), fast_exp2(t2.y));
-              }
-              // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
-              // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
-              const __half2 h2 = __floats2half2_rn(ex.x, ex.y);
-              packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
-            }
-            tmem_st16(t_wg + TM_P + 16 * half, packed);
-          }
-        };
-#if B200_SPEC
-        // Nothing in the exponentials below depends on this step's maximum: they use the
-        // offset the earlier steps settled on, so the MUFU work, the packed fmas and the
-        // max reduction are independent instruction streams the scheduler can interleave.
-        // The offset only has to move when the maximum grew past the rescale threshold,
-        // which is rare after the first step of an item; then the step's P is redone.
-        const bool have_offset = (t > 0) || p.resume;
-        if (have_offset) emit_p(m_used);
-#endif
         // four independent chains, so the reduction is not one 32-deep dependency
         float mxa = fmaxf(u[0].x, u[0].y), mxb = fmaxf(u[1].x, u[1].y);
         float mxc = fmaxf(u[2].x, u[2].y), mxd = fmaxf(u[3].x, u[3].y);
@@ -523,24 +504,49 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mxc = fmax3(mxc, u[e + 2].x, u[e + 2].y);
           mxd = fmax3(mxd, u[e + 3].x, u[e + 3].y);
         }
-        const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
-        const float m_new = fmaxf(m_run, mx);
-        m_run = m_new;
-        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
+        const float mx2 = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd)) * LOG2E;  // this step's maximum, log2 units
+        // Lazy rescale: the offset only moves when this step's maximum exceeds it by more than
+        // 2^8 (then it exceeds every earlier maximum too, which stayed within the threshold).
+        const bool need = (mx2 - m2_used) > RESCALE_THRESHOLD;  // true on the first step (m2_used = -inf)
         float alpha = 1.f;
         if (need) {
-          alpha = fast_exp2((m_used - m_new) * LOG2E);  // 0 on the first step (m_used = -inf)
-          m_used = m_new;
+          const float m2_new = rintf(mx2);
+          alpha = fast_exp2(m2_used - m2_new);  // an exact power of two; 0 on the first step
+          m2_used = m2_new;
         }
         const bool any_need = __any_sync(0xffffffffu, need);
-#if B200_SPEC
-        if (!have_offset || any_need) {
-          if (have_offset) tmem_st_wait();  // the speculative P is overwritten in order
-          emit_p(m_used);
+        // exp(u - m) = 2^(u * log2e - m2): one fma per pair feeds the MUFU unit (|m2| < 2^17, so
+        // the sum is exact to the last bit of the product and cancels exactly for the keys that
+        // equal the offset). B200_POLY of every 16 pairs take the polynomial path instead: the
+        // MUFU unit delivers 16 results per clock and SM and would otherwise be the one pipe
+        // every exponential queues for, while the FMA pipe idles.
+        // P goes to TMEM in two halves of 32 keys to keep the live registers down.
+        {
+          const float2 log2e2 = make_float2(LOG2E, LOG2E);
+          const float2 nm2 = make_float2(-m2_used, -m2_used);
+          const float2 mm2 = make_float2(EXP_MAGIC - m2_used, EXP_MAGIC - m2_used);
+          const float u_min = (m2_used - 120.0f) * LN2;  // keeps the polynomial path's t above about -120
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float2 ue = u[16 * half + e];
+              float2 ex;
+              if (((e + 1) * B200_POLY) / 16 != (e * B200_POLY) / 16) {  // spread evenly over the half
+                ex = poly_exp2x2(make_float2(fmaxf(ue.x, u_min), fmaxf(ue.y, u_min)), log2e2, mm2);
+              } else {
+                const float2 t2 = __ffma2_rn(ue, log2e2, nm2);
+                ex = make_float2(fast_exp2(t2.x), fast_exp2(t2.y));
+              }
+              // fp32 exponentials, rounded once to the fp16 pair the tensor core reads
+              // (the packed fp16 ex2 costs more instructions than two fp32 ones here)
+              const __half2 h2 = __floats2half2_rn(ex.x, ex.y);
+              packed[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            tmem_st16(t_wg + TM_P + 16 * half, packed);
+          }
         }
-#else
-        emit_p(m_used);
-#endif
 #if B200_TURNS
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.turn[(wg + 1) % NWG][quarter]);
@@ -597,7 +603,7 @@ att_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                   __uint_as_float(o[4 * q4 + 2]), __uint_as_float(o[4 * q4 + 3]));
         }
         if (p.row_max) {
-          p.row_max[si] = m_used;
+          p.row_max[si] = m2_used * LN2;  // natural-log units
           p.row_sum[si] = l;
         }
       }
@@ -639,86 +645,110 @@ extern "C" size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k) 
   return static_cast<size_t>(n_i) * b200::round_up(n_k, 64) * sizeof(float) + 1024;
 }
 
-namespace {
-// `may_time` = false keeps the launch free of event creation whatever the timing switch
-// says at that moment (the allocation-free entry point relies on it).
-int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, bool may_time);
-}  // namespace
-
-extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_stream_t stream) {
-  return core_launch(a, stream, true);
+extern "C" size_t b200tri_triatt_core_multi_workspace_bytes(int32_t n_i, int32_t n_k, int32_t n_tiles) {
+  if (n_tiles <= 0) return 0;
+  return static_cast<size_t>(n_tiles) * b200tri_triatt_core_workspace_bytes(n_i, n_k);
 }
 
 namespace {
-int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, bool may_time) {
+// `may_time` = false keeps the launch free of event creation whatever the timing switch
+// says at that moment (the allocation-free entry point relies on it).
+int core_launch(const b200tri_triatt_core_args* tiles, int n_tiles, b200tri_stream_t stream_, bool may_time);
+}  // namespace
+
+extern "C" int b200tri_triatt_core(const b200tri_triatt_core_args* a, b200tri_stream_t stream) {
+  return core_launch(a, 1, stream, true);
+}
+
+extern "C" int b200tri_triatt_core_multi(const b200tri_triatt_core_args* tiles, int32_t n_tiles,
+                                         b200tri_stream_t stream) {
+  return core_launch(tiles, n_tiles, stream, true);
+}
+
+namespace {
+int core_launch(const b200tri_triatt_core_args* tiles, int n_tiles, b200tri_stream_t stream_, bool may_time) {
   using namespace b200;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "att core: null args");
-  B200_REQUIRE(a->q && a->k && a->vt && a->bias && (a->o || a->unnormalized), B200TRI_ERR_INVALID,
-               "att core: null pointer argument");
+  B200_REQUIRE(tiles != nullptr, B200TRI_ERR_INVALID, "att core: null args");
+  B200_REQUIRE(n_tiles >= 1 && n_tiles <= MAX_KEY_TILES, B200TRI_ERR_INVALID,
+               "att core: 1..%d key tiles per launch (got %d)", MAX_KEY_TILES, n_tiles);
+  const b200tri_triatt_core_args* a = tiles;  // queries, sizes, outputs and flags come from the first entry
+  B200_REQUIRE(a->q && (a->o || a->unnormalized), B200TRI_ERR_INVALID, "att core: null pointer argument");
   B200_REQUIRE(a->n_i > 0 && a->n_j > 0 && a->n_k > 0, B200TRI_ERR_INVALID, "att core: sizes must be positive");
   B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
                "att core: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
-  B200_REQUIRE(a->v_ld % 8 == 0 && a->bias_ld % 8 == 0 && a->bias_head_stride % 8 == 0 && a->v_ld >= a->n_k &&
-                   a->bias_ld >= a->n_k,
-               B200TRI_ERR_INVALID, "att core: pitches must be multiples of 8 elements and cover n_k");
   B200_REQUIRE((a->row_max == nullptr) == (a->row_sum == nullptr), B200TRI_ERR_INVALID,
                "att core: row_max and row_sum go together");
   B200_REQUIRE((reinterpret_cast<uintptr_t>(a->o) & 15) == 0, B200TRI_ERR_INVALID, "att core: o must be 16-byte aligned");
   B200_REQUIRE(!(a->unnormalized || a->resume) ||
                    (a->acc_o && a->row_max && a->row_sum && (reinterpret_cast<uintptr_t>(a->acc_o) & 15) == 0),
                B200TRI_ERR_INVALID, "att core: resume/unnormalized need acc_o (16-byte aligned), row_max and row_sum");
-  const size_t need = b200tri_triatt_core_workspace_bytes(a->n_i, a->n_k);
-  B200_REQUIRE(a->workspace && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
-               "att core: workspace of %zu bytes needed", need);
+  B200_REQUIRE(n_tiles == 1 || a->n_k % KT == 0, B200TRI_ERR_INVALID,
+               "att core: with several key tiles n_k must be a multiple of %d (got %d)", KT, a->n_k);
+  const size_t need_one = b200tri_triatt_core_workspace_bytes(a->n_i, a->n_k);
+  B200_REQUIRE(a->workspace && a->workspace_bytes >= need_one * n_tiles, B200TRI_ERR_WORKSPACE,
+               "att core: workspace of %zu bytes needed", need_one * n_tiles);
   int* status = device_status_word();
   B200_REQUIRE(status != nullptr, B200TRI_ERR_CUDA, "att core: no current CUDA device");
 
-  Carver ws(a->workspace);
   const int ldm = round_up(a->n_k, 64);
-  float* mb = ws.take<float>(static_cast<size_t>(a->n_i) * ldm);
-  {
-    const long long total = static_cast<long long>(a->n_i) * ldm;
-    count_launch();
-    mask_bias_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-        a->mask, a->ms_i, a->ms_k, a->n_i, a->n_k, ldm, a->inf, a->mask_additive ? 1 : 0, mb);
-    B200_CUDA_OK(cudaGetLastError());
+  TileMaps tm;
+  for (int t = 0; t < n_tiles; ++t) {
+    const b200tri_triatt_core_args* ti = tiles + t;
+    B200_REQUIRE(ti->k && ti->vt && ti->bias, B200TRI_ERR_INVALID, "att core: null k/vt/bias in key tile %d", t);
+    B200_REQUIRE(ti->n_k == a->n_k, B200TRI_ERR_INVALID, "att core: key tiles of one launch must have the same n_k");
+    B200_REQUIRE(ti->v_ld % 8 == 0 && ti->bias_ld % 8 == 0 && ti->bias_head_stride % 8 == 0 && ti->v_ld >= a->n_k &&
+                     ti->bias_ld >= a->n_k,
+                 B200TRI_ERR_INVALID, "att core: pitches must be multiples of 8 elements and cover n_k");
+    float* mb = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + need_one * t);
+    {
+      const long long total = static_cast<long long>(a->n_i) * ldm;
+      count_launch();
+      mask_bias_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+          ti->mask, ti->ms_i, ti->ms_k, a->n_i, a->n_k, ldm, ti->inf, ti->mask_additive ? 1 : 0, mb);
+      B200_CUDA_OK(cudaGetLastError());
+    }
+    {
+      const uint64_t dims[3] = {128, (uint64_t)a->n_k, (uint64_t)a->n_i};
+      const uint64_t str[2] = {256, (uint64_t)a->n_k * 256};
+      const uint32_t box[3] = {32, KT, 1};
+      int rc = make_tmap(&tm.k[t], ti->k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B64);
+      if (rc) return rc;
+    }
+    {
+      const uint64_t dims[3] = {(uint64_t)a->n_k, 128, (uint64_t)a->n_i};
+      const uint64_t str[2] = {(uint64_t)ti->v_ld * 2, (uint64_t)ti->v_ld * 2 * 128};
+      const uint32_t box[3] = {KT, 32, 1};
+      int rc = make_tmap(&tm.v[t], ti->vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, str, box, Swz::B128);
+      if (rc) return rc;
+    }
+    {
+      const uint64_t dims[3] = {(uint64_t)a->n_k, (uint64_t)a->n_j, 4};
+      const uint64_t str[2] = {(uint64_t)ti->bias_ld * 2, (uint64_t)ti->bias_head_stride * 2};
+      const uint32_t box[3] = {KT, 128, 1};
+      int rc = make_tmap(&tm.b[t], ti->bias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+      if (rc) return rc;
+    }
+    {
+      const uint64_t dims[2] = {(uint64_t)ldm, (uint64_t)a->n_i};
+      const uint64_t str[1] = {(uint64_t)ldm * 4};
+      const uint32_t box[2] = {KT, 1};
+      int rc = make_tmap(&tm.m[t], mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dims, str, box, Swz::None);
+      if (rc) return rc;
+    }
   }
-
-  CUtensorMap tm_q, tm_k, tm_v, tm_b, tm_m;
+  for (int t = n_tiles; t < MAX_KEY_TILES; ++t) {  // unused slots: valid descriptors, never read
+    tm.k[t] = tm.k[0];
+    tm.v[t] = tm.v[0];
+    tm.b[t] = tm.b[0];
+    tm.m[t] = tm.m[0];
+  }
+  CUtensorMap tm_q;
   {
     const uint64_t dims[3] = {128, (uint64_t)a->n_j, (uint64_t)a->n_i};
     const uint64_t str[2] = {256, (uint64_t)a->n_j * 256};
     const uint32_t box[3] = {32, 128, 1};
     int rc = make_tmap(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B64);
-    if (rc) return rc;
-  }
-  {
-    const uint64_t dims[3] = {128, (uint64_t)a->n_k, (uint64_t)a->n_i};
-    const uint64_t str[2] = {256, (uint64_t)a->n_k * 256};
-    const uint32_t box[3] = {32, KT, 1};
-    int rc = make_tmap(&tm_k, a->k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B64);
-    if (rc) return rc;
-  }
-  {
-    const uint64_t dims[3] = {(uint64_t)a->n_k, 128, (uint64_t)a->n_i};
-    const uint64_t str[2] = {(uint64_t)a->v_ld * 2, (uint64_t)a->v_ld * 2 * 128};
-    const uint32_t box[3] = {KT, 32, 1};
-    int rc = make_tmap(&tm_v, a->vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, str, box, Swz::B128);
-    if (rc) return rc;
-  }
-  {
-    const uint64_t dims[3] = {(uint64_t)a->n_k, (uint64_t)a->n_j, 4};
-    const uint64_t str[2] = {(uint64_t)a->bias_ld * 2, (uint64_t)a->bias_head_stride * 2};
-    const uint32_t box[3] = {KT, 128, 1};
-    int rc = make_tmap(&tm_b, a->bias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
-    if (rc) return rc;
-  }
-  {
-    const uint64_t dims[2] = {(uint64_t)ldm, (uint64_t)a->n_i};
-    const uint64_t str[1] = {(uint64_t)ldm * 4};
-    const uint32_t box[2] = {KT, 1};
-    int rc = make_tmap(&tm_m, mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dims, str, box, Swz::None);
     if (rc) return rc;
   }
   Params p;
@@ -728,7 +758,8 @@ int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, boo
   p.heads = a->heads;
   p.groups = (a->n_i + NWG - 1) / NWG;
   p.tiles_j = (a->n_j + 127) / 128;
-  p.steps = (a->n_k + KT - 1) / KT;
+  p.steps_per_tile = (a->n_k + KT - 1) / KT;
+  p.steps = p.steps_per_tile * n_tiles;
   p.total_items = static_cast<long long>(a->heads) * p.groups * p.tiles_j;
   p.o = static_cast<__nv_bfloat16*>(a->o);
   p.row_max = a->row_max;
@@ -746,7 +777,7 @@ int core_launch(const b200tri_triatt_core_args* a, b200tri_stream_t stream_, boo
   {
     TimedLaunch timed(K_TRIATT_CORE, stream, may_time);
     count_launch();
-    att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm_k, tm_v, tm_b, tm_m, p);
+    att_core_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_q, tm, p);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;
@@ -802,5 +833,5 @@ extern "C" int b200tri_triatt_core_static(const b200tri_triatt_core_args* a, b20
   b200tri_triatt_core_args local = *a;
   local.workspace = scratch;
   local.workspace_bytes = sizeof(float) * static_cast<size_t>(B200TRI_TRIATT_CORE_STATIC_MAX_FLOATS + 256);
-  return core_launch(&local, stream, false);
+  return core_launch(&local, 1, stream, false);
 }

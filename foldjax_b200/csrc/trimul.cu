@@ -50,11 +50,29 @@ extern "C" size_t b200tri_trimul_workspace_bytes(int32_t n) {
   return plan_offsets(n).total;
 }
 
+extern "C" size_t b200tri_trimul_workspace_bytes_dtype(int32_t n, int32_t dtype) {
+  if (dtype == B200TRI_DTYPE_F32) return b200::trimul_workspace_bytes_f32(n);
+  return dtype == B200TRI_DTYPE_BF16 ? b200tri_trimul_workspace_bytes(n) : 0;
+}
+
 extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stream_t stream) {
   using namespace b200;
   B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "trimul: null args");
   B200_REQUIRE(a->n > 0, B200TRI_ERR_INVALID, "trimul: n must be positive (got %d)", a->n);
   B200_REQUIRE(a->x && a->out, B200TRI_ERR_INVALID, "trimul: x/out must not be null");
+  B200_REQUIRE(a->dtype == B200TRI_DTYPE_BF16 || a->dtype == B200TRI_DTYPE_F32, B200TRI_ERR_UNSUPPORTED,
+               "trimul: unknown dtype %d", a->dtype);
+  if (a->dtype == B200TRI_DTYPE_F32) {
+    const size_t need = trimul_workspace_bytes_f32(a->n);
+    B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
+                 "trimul (float32): workspace of %zu bytes needed for n=%d, got %zu", need, a->n, a->workspace_bytes);
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
+                 "trimul: workspace must be 1024-byte aligned");
+    B200_REQUIRE(a->norm_in_scale && a->norm_in_bias && a->p_in && a->g_in && a->norm_out_scale && a->norm_out_bias &&
+                     a->p_out && a->g_out,
+                 B200TRI_ERR_INVALID, "trimul: null parameter pointer");
+    return trimul_forward_f32(a, reinterpret_cast<cudaStream_t>(stream));
+  }
   const Plan pl = plan_offsets(a->n);
   B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,
                "trimul: workspace of %zu bytes needed for n=%d, got %zu", pl.total, a->n, a->workspace_bytes);

@@ -37,13 +37,27 @@ def _check_pair(x: torch.Tensor) -> tuple[torch.Tensor, bool]:
     return x, squeeze
 
 
-def _leaf(params: Mapping, *path: str) -> torch.Tensor:
+def _leaf(params: Mapping, *path: str, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     node: Any = params
     for key in path:
         node = node[key]
-    if not isinstance(node, torch.Tensor) or not node.is_cuda or node.dtype != torch.bfloat16:
-        node = dev.to_device(node, torch.bfloat16)
+    if not isinstance(node, torch.Tensor) or not node.is_cuda or node.dtype != dtype:
+        node = dev.to_device(node, dtype)
     return node.contiguous()
+
+
+def resolve_dtype(x: Any, dtype: str | None) -> tuple[torch.dtype, int]:
+    """Trunk dtype of a call: ``dtype`` if given ("bfloat16" / "float32"), else float32 for a
+    float32 CUDA tensor and bfloat16 for everything else (host arrays are float32 containers
+    of either trunk, so they say nothing). Returns (torch dtype, the C ABI's dtype code)."""
+    if dtype is None:
+        dtype = "float32" if isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32 else "bfloat16"
+    name = {"bf16": "bfloat16", "fp32": "float32"}.get(str(dtype), str(dtype))
+    if name == "bfloat16":
+        return torch.bfloat16, _lib.DTYPE_BF16
+    if name == "float32":
+        return torch.float32, _lib.DTYPE_F32
+    raise ValueError(f"Unsupported dtype: {dtype!r} (expected 'bfloat16' or 'float32')")
 
 
 def triangle_multiplication_forward(
@@ -58,11 +72,15 @@ def triangle_multiplication_forward(
     *,
     residual: Any | None = None,
     out: torch.Tensor | None = None,
+    dtype: str | None = None,
 ):
     """Boltz triangle multiplication, outgoing or incoming.
 
-    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``) in bf16, ``mask`` is
-    ``[B, N, N]`` or None. Device tensors in -> device tensor out; NumPy / CPU
+    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``), ``mask`` is ``[B, N, N]`` or None.
+    ``dtype`` selects the trunk: "bfloat16" (default; bf16 storage, fp32 accumulation) or
+    "float32" (every step in float32, the contraction as split-bf16 products on the tensor
+    cores; the reference's float32 trunk, 1e-4). A float32 CUDA tensor selects float32 by
+    itself. Device tensors in -> device tensor out; NumPy / CPU
     tensors in -> the inputs are copied to the GPU, the result is copied back and
     returned as the same kind of array (the end-to-end path).
 
@@ -80,7 +98,8 @@ def triangle_multiplication_forward(
     lib = _lib.load()
     host_in = dev.is_host_array(x)
     numpy_in = isinstance(x, np.ndarray)
-    xd, squeeze = _check_pair(dev.to_device(x, torch.bfloat16))
+    tdt, code = resolve_dtype(x, dtype)
+    xd, squeeze = _check_pair(dev.to_device(x, tdt))
     b, n = xd.shape[0], xd.shape[1]
     md = None
     if mask is not None:
@@ -91,7 +110,7 @@ def triangle_multiplication_forward(
             raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
     rd = None
     if residual is not None:
-        rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+        rd, _ = _check_pair(dev.to_device(residual, tdt))
         dev.check_same_shape(rd, xd, "residual")
     if out is None:
         out = torch.empty_like(xd)
@@ -100,25 +119,25 @@ def triangle_multiplication_forward(
             out = out.unsqueeze(0)
         dev.check_out(out, xd)
     leaves = {
-        "norm_in_scale": _leaf(params, "norm_in", "scale"),
-        "norm_in_bias": _leaf(params, "norm_in", "bias"),
-        "p_in": _leaf(params, "p_in", "kernel"),
-        "g_in": _leaf(params, "g_in", "kernel"),
-        "norm_out_scale": _leaf(params, "norm_out", "scale"),
-        "norm_out_bias": _leaf(params, "norm_out", "bias"),
-        "p_out": _leaf(params, "p_out", "kernel"),
-        "g_out": _leaf(params, "g_out", "kernel"),
+        "norm_in_scale": _leaf(params, "norm_in", "scale", dtype=tdt),
+        "norm_in_bias": _leaf(params, "norm_in", "bias", dtype=tdt),
+        "p_in": _leaf(params, "p_in", "kernel", dtype=tdt),
+        "g_in": _leaf(params, "g_in", "kernel", dtype=tdt),
+        "norm_out_scale": _leaf(params, "norm_out", "scale", dtype=tdt),
+        "norm_out_bias": _leaf(params, "norm_out", "bias", dtype=tdt),
+        "p_out": _leaf(params, "p_out", "kernel", dtype=tdt),
+        "g_out": _leaf(params, "g_out", "kernel", dtype=tdt),
     }
     if tuple(leaves["p_in"].shape) != (C_Z, 2 * C_Z) or tuple(leaves["p_out"].shape) != (C_Z, C_Z):
         raise ValueError("libb200tri is built for hidden width 128 (p_in [128,256], p_out [128,128])")
-    nbytes = lib.b200tri_trimul_workspace_bytes(n)
+    nbytes = lib.b200tri_trimul_workspace_bytes_dtype(n, code)
     ws = dev.workspace(nbytes, "trimul")
     for bi in range(b):
         args = _lib.TrimulArgs(
             n=n, incoming=int(direction == "incoming"), eps=float(eps),
             x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
             residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
-            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code,
             **{k: v.data_ptr() for k, v in leaves.items()},
         )
         _lib.check(lib.b200tri_trimul_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))

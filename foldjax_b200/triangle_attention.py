@@ -18,7 +18,7 @@ import torch
 
 from . import _device as dev
 from . import _lib
-from .triangle import C_Z, _check_pair, _leaf, _ptr
+from .triangle import C_Z, _check_pair, _leaf, _ptr, resolve_dtype
 
 HEADS = 4
 HEAD_DIM = 32
@@ -38,11 +38,14 @@ def triangle_attention_forward(
     *,
     residual: Any | None = None,
     out: torch.Tensor | None = None,
+    dtype: str | None = None,
 ):
     """Boltz TriangleAttention, starting or ending node.
 
-    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``) bf16, ``mask`` ``[B, N, N]`` or
-    None (= ones). ``params`` is the reference's mapping ``{"layer_norm": {scale,
+    ``x`` is ``[B, N, N, 128]`` (or ``[N, N, 128]``), ``mask`` ``[B, N, N]`` or None (= ones).
+    ``dtype`` selects the trunk: "bfloat16" (default) or "float32" (every step in float32 on
+    the CUDA cores, the reference's float32 trunk, 1e-4); a float32 CUDA tensor selects
+    float32 by itself. ``params`` is the reference's mapping ``{"layer_norm": {scale,
     bias}, "linear": {kernel [128, 4]}, "mha": {"linear_q" | "linear_k" |
     "linear_v" | "linear_g" | "linear_o": {kernel [128, 128]}}}``. Device tensors in
     -> device tensor out; NumPy / CPU tensors in -> copied to the GPU and back.
@@ -55,7 +58,8 @@ def triangle_attention_forward(
     lib = _lib.load()
     host_in = dev.is_host_array(x)
     numpy_in = isinstance(x, np.ndarray)
-    xd, squeeze = _check_pair(dev.to_device(x, torch.bfloat16))
+    tdt, code = resolve_dtype(x, dtype)
+    xd, squeeze = _check_pair(dev.to_device(x, tdt))
     b, n = xd.shape[0], xd.shape[1]
     md = None
     if mask is not None:
@@ -66,7 +70,7 @@ def triangle_attention_forward(
             raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
     rd = None
     if residual is not None:
-        rd, _ = _check_pair(dev.to_device(residual, torch.bfloat16))
+        rd, _ = _check_pair(dev.to_device(residual, tdt))
         dev.check_same_shape(rd, xd, "residual")
     if out is None:
         out = torch.empty_like(xd)
@@ -75,25 +79,25 @@ def triangle_attention_forward(
             out = out.unsqueeze(0)
         dev.check_out(out, xd)
     leaves = {
-        "norm_scale": _leaf(params, "layer_norm", "scale"),
-        "norm_bias": _leaf(params, "layer_norm", "bias"),
-        "w_bias": _leaf(params, "linear", "kernel"),
-        "w_q": _leaf(params, "mha", "linear_q", "kernel"),
-        "w_k": _leaf(params, "mha", "linear_k", "kernel"),
-        "w_v": _leaf(params, "mha", "linear_v", "kernel"),
-        "w_g": _leaf(params, "mha", "linear_g", "kernel"),
-        "w_o": _leaf(params, "mha", "linear_o", "kernel"),
+        "norm_scale": _leaf(params, "layer_norm", "scale", dtype=tdt),
+        "norm_bias": _leaf(params, "layer_norm", "bias", dtype=tdt),
+        "w_bias": _leaf(params, "linear", "kernel", dtype=tdt),
+        "w_q": _leaf(params, "mha", "linear_q", "kernel", dtype=tdt),
+        "w_k": _leaf(params, "mha", "linear_k", "kernel", dtype=tdt),
+        "w_v": _leaf(params, "mha", "linear_v", "kernel", dtype=tdt),
+        "w_g": _leaf(params, "mha", "linear_g", "kernel", dtype=tdt),
+        "w_o": _leaf(params, "mha", "linear_o", "kernel", dtype=tdt),
     }
     if tuple(leaves["w_bias"].shape) != (C_Z, HEADS) or tuple(leaves["w_q"].shape) != (C_Z, HEADS * HEAD_DIM):
         raise ValueError("libb200tri is built for 4 heads x 32 (linear [128,4], linear_q [128,128])")
-    nbytes = lib.b200tri_triatt_workspace_bytes(n)
+    nbytes = lib.b200tri_triatt_workspace_bytes_dtype(n, code)
     ws = dev.workspace(nbytes, "triatt")
     for bi in range(b):
         args = _lib.TriattArgs(
             n=n, starting=int(bool(starting)), heads=HEADS, head_dim=HEAD_DIM, inf=float(inf), eps=float(eps),
             x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
             residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
-            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code,
             **{k: v.data_ptr() for k, v in leaves.items()},
         )
         _lib.check(lib.b200tri_triatt_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))

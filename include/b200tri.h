@@ -26,6 +26,13 @@ extern "C" {
 
 typedef struct CUstream_st* b200tri_stream_t; /* == cudaStream_t */
 
+/* Element type of the pair tensor, the parameters and the result of the two triangle ops.
+ * BF16 is the throughput mode (bf16 storage, float32 accumulation, the reference's bf16
+ * trunk); F32 is the float32 trunk of the reference - every step in float32, the triangle
+ * contraction as split-bf16 products accumulated in float32 on the tensor cores - and meets
+ * its 1e-4 tolerance. */
+enum { B200TRI_DTYPE_BF16 = 0, B200TRI_DTYPE_F32 = 1 };
+
 enum {
   B200TRI_OK = 0,
   B200TRI_ERR_INVALID = 1,     /* bad argument (null pointer, alignment, size) */
@@ -105,9 +112,12 @@ typedef struct {
   void* out;            /* [n, n, 128] */
   void* workspace;
   size_t workspace_bytes;
+  int32_t dtype; /* B200TRI_DTYPE_*: type of x, mask excepted (always float32), of every
+                    parameter, of residual and of out. 0 = bf16. */
 } b200tri_trimul_args;
 
-size_t b200tri_trimul_workspace_bytes(int32_t n);
+size_t b200tri_trimul_workspace_bytes(int32_t n); /* bf16 */
+size_t b200tri_trimul_workspace_bytes_dtype(int32_t n, int32_t dtype);
 int b200tri_trimul_forward(const b200tri_trimul_args* args, b200tri_stream_t stream);
 
 /* The three stages of the update, exposed so that the 2-D context-parallel
@@ -231,9 +241,11 @@ typedef struct {
   void* out;
   void* workspace;
   size_t workspace_bytes;
+  int32_t dtype; /* B200TRI_DTYPE_*, as in b200tri_trimul_args */
 } b200tri_triatt_args;
 
-size_t b200tri_triatt_workspace_bytes(int32_t n);
+size_t b200tri_triatt_workspace_bytes(int32_t n); /* bf16 */
+size_t b200tri_triatt_workspace_bytes_dtype(int32_t n, int32_t dtype);
 int b200tri_triatt_forward(const b200tri_triatt_args* args, b200tri_stream_t stream);
 
 /* Stages, exposed for the context-parallel ring (the reference's
@@ -309,6 +321,16 @@ typedef struct {
 size_t b200tri_triatt_core_workspace_bytes(int32_t n_i, int32_t n_k);
 int b200tri_triatt_core(const b200tri_triatt_core_args* args, b200tri_stream_t stream);
 
+/* core over several key tiles in ONE launch: the same softmax walks tiles[0..n_tiles) in
+ * order, each tile with its own k, vt, bias and mask buffers (the peers' tiles of a
+ * context-parallel ring, which live in separate receive buffers); q, the sizes, the
+ * outputs, the flags and the workspace are taken from tiles[0]. All tiles have the same
+ * n_k, a multiple of 64 when n_tiles > 1; at most 7 tiles per launch. The running state
+ * stays on chip between tiles, which the one-launch-per-tile form has to spill to acc_o.
+ * Replaces the per-hop update of local_ring, src/foldjax/models/_cp_attention.py:290-386. */
+size_t b200tri_triatt_core_multi_workspace_bytes(int32_t n_i, int32_t n_k, int32_t n_tiles);
+int b200tri_triatt_core_multi(const b200tri_triatt_core_args* tiles, int32_t n_tiles, b200tri_stream_t stream);
+
 /* core, for callers that have no scratch memory to give and must not allocate.
  * This entry point has no counterpart in the reference. Some hosts of this
  * library cannot hand over a workspace: a custom-call handler inside a framework
@@ -358,6 +380,108 @@ typedef struct {
 
 size_t b200tri_triatt_finish_workspace_bytes(void);
 int b200tri_triatt_finish(const b200tri_triatt_finish_args* args, b200tri_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * 2-D context parallelism: the pair tensor tiled z[I_r, J_c] over an R x C grid of GPUs
+ * (C a multiple of R: 1x2, 2x2, 2x4 on one 8-GPU box), one communicator per GPU.
+ * Replaces: context_parallel / resolve_cp_layout, src/foldjax/models/_cp.py:162-187,259;
+ *   _cannon_contract, src/foldjax/models/boltz2/models/triangle/triangle.py:132-212;
+ *   ring_triangle_attention_2d, src/foldjax/models/_cp_attention.py:197-403 and its
+ *   callers (boltz2 triangle_attention_cp.py:40-156, protenix triangle_attention_cp.py:33,
+ *   openfold3 triangle_attention_cp.py:30).
+ * rank = r * cols + c owns rows I_r (n / rows of them) and columns J_c (n / cols).
+ * Tiles travel over NVLink as grouped ncclSend/ncclRecv on the communicator's own stream,
+ * fenced against the caller's stream by events: every entry point below only enqueues.
+ * NCCL (libnccl.so.2) is loaded on first use of this section.
+ *
+ * One process per GPU: rank 0 calls b200tri_comm_unique_id, the caller hands the 128 bytes
+ * to every rank (any side channel), each rank makes its device current and calls
+ * b200tri_comm_init. One process driving all GPUs (the reference's arrangement under
+ * shard_map): b200tri_comm_init_all fills comms[0..world); calls for different devices come
+ * from one host thread per device, or are wrapped in b200tri_comm_group_start/_end.
+ * --------------------------------------------------------------------- */
+#define B200TRI_COMM_ID_BYTES 128
+typedef struct b200tri_comm b200tri_comm;
+
+int b200tri_comm_unique_id(void* id128);
+int b200tri_comm_init(b200tri_comm** comm, const void* id128, int32_t world, int32_t rank, int32_t rows, int32_t cols);
+int b200tri_comm_init_all(b200tri_comm** comms, const int32_t* devices, int32_t world, int32_t rows, int32_t cols);
+int b200tri_comm_destroy(b200tri_comm* comm);
+int b200tri_comm_info(const b200tri_comm* comm, int32_t* world, int32_t* rank, int32_t* rows, int32_t* cols);
+int b200tri_comm_group_start(void);
+int b200tri_comm_group_end(void);
+
+/* Mesh self-test, the counterpart of verify_mesh_exchange (src/foldjax/models/_cp.py:199-232):
+ * every rank sends `bytes` from `shard` to every other rank and receives theirs into
+ * gathered[src * bytes ...] through the very send/receive path the ops use. The caller stamps
+ * the shards, copies `gathered` to the host and judges it there. */
+int b200tri_comm_probe(b200tri_comm* comm, const void* shard, void* gathered, size_t bytes, b200tri_stream_t stream);
+
+/* The exchange schedule, for inspection and tests: the global message list of an op on a
+ * rows x cols grid. A message moves `what` (0 = a, 1 = b, 2 = K and V, 3 = pair bias) of rank
+ * `src` - row block `block` of it, or all of it when block = -1 - into slot (slot0, slot1) of
+ * rank `dst`'s panel; src == dst is a local copy. Returns the number of messages (writes at
+ * most `capacity` of them to `out`, which may be NULL), or -1 on a bad grid / op. */
+enum { B200TRI_CP_TRIMUL_OUTGOING = 0, B200TRI_CP_TRIMUL_INCOMING = 1, B200TRI_CP_TRIATT_STARTING = 2,
+       B200TRI_CP_TRIATT_ENDING = 3 };
+typedef struct { int32_t src, dst, what, block, slot0, slot1; } b200tri_cp_msg;
+int b200tri_cp_plan(int32_t rows, int32_t cols, int32_t op, b200tri_cp_msg* out, int32_t capacity);
+
+/* Triangle multiplication on this rank's tile. x / residual / out are the rank's tile
+ * [n / rows][n / cols][128] bf16; mask is the WHOLE [n][n] float32 mask (or NULL), replicated
+ * on every rank; parameters as in b200tri_trimul_args. n must be a multiple of cols (pad
+ * with zero pairs and mask 0, as the reference does, triangle.py:165-172). */
+typedef struct {
+  int32_t n;        /* tokens of the whole pair tensor */
+  int32_t incoming;
+  float eps;
+  const void* x;
+  const float* mask;
+  const void* norm_in_scale;
+  const void* norm_in_bias;
+  const void* p_in;
+  const void* g_in;
+  const void* norm_out_scale;
+  const void* norm_out_bias;
+  const void* p_out;
+  const void* g_out;
+  const void* residual;
+  void* out;
+  void* workspace; /* b200tri_trimul_cp_workspace_bytes(comm, n), 1 KiB aligned */
+  size_t workspace_bytes;
+} b200tri_trimul_cp_args;
+
+size_t b200tri_trimul_cp_workspace_bytes(const b200tri_comm* comm, int32_t n);
+int b200tri_trimul_cp(b200tri_comm* comm, const b200tri_trimul_cp_args* args, b200tri_stream_t stream);
+
+/* Triangle attention on this rank's tile: the starting node rings over the key tiles of
+ * the rank's grid row, the ending node over those of its grid column. One softmax is
+ * continued over the key tiles (own tile first while the peers' K/V are in flight, then all
+ * peer tiles in one launch). Rows without a valid key come out as the uniform average over
+ * their keys (the convention of the dense path), not as the zeros of the reference's ring. */
+typedef struct {
+  int32_t n;
+  int32_t starting;
+  int32_t heads, head_dim; /* 4 x 32 */
+  float inf, eps;
+  const void* x;
+  const float* mask; /* whole [n][n] or NULL */
+  const void* norm_scale;
+  const void* norm_bias;
+  const void* w_bias;
+  const void* w_q;
+  const void* w_k;
+  const void* w_v;
+  const void* w_g;
+  const void* w_o;
+  const void* residual;
+  void* out;
+  void* workspace; /* b200tri_triatt_cp_workspace_bytes(comm, n), 1 KiB aligned */
+  size_t workspace_bytes;
+} b200tri_triatt_cp_args;
+
+size_t b200tri_triatt_cp_workspace_bytes(const b200tri_comm* comm, int32_t n);
+int b200tri_triatt_cp(b200tri_comm* comm, const b200tri_triatt_cp_args* args, b200tri_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Pair transition (the feed-forward that follows the triangle ops in a

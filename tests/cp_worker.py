@@ -1,8 +1,9 @@
 """Worker for the multi-GPU context-parallel tests (launched by torchrun).
 
 Every rank builds the same seeded full-size problem, keeps its own tile, runs the
-context-parallel op, and rank 0 gathers the tiles and compares them with the
-single-GPU kernels on the full tensor (and, at small N, with the CPU oracle).
+context-parallel op through the C ABI (b200tri_trimul_cp / b200tri_triatt_cp), and rank 0
+gathers the tiles and compares them with the single-GPU kernels on the full tensor and, at
+N <= 256, with the CPU oracle's bf16 emulation of the reference.
 Exit code 0 = all comparisons passed.
 """
 
@@ -28,6 +29,7 @@ def main() -> int:
     from foldjax_b200.synthetic import block_params, pad_mask, triatt_params, trimul_params
     from foldjax_b200.triangle import triangle_multiplication_forward
     from foldjax_b200.triangle_attention import triangle_attention_forward
+    from oracle import triangle_oracle as orc  # the checker, at small N
 
     n = int(os.environ.get("CP_TEST_TOKENS", "512"))
     local = int(os.environ["LOCAL_RANK"])
@@ -36,8 +38,10 @@ def main() -> int:
     ctx = cp.context_parallel()
     grid = ctx.grid
     rng = np.random.default_rng(7)
-    pm = dev.params_to_device(trimul_params(rng, std=0.05))
-    pa = dev.params_to_device(triatt_params(rng, std=0.05))
+    pm_np, pa_np = trimul_params(rng, std=0.05), triatt_params(rng, std=0.05)
+    pm_np, pa_np = orc.round_params(pm_np, "bfloat16"), orc.round_params(pa_np, "bfloat16")
+    pm = dev.params_to_device(pm_np)
+    pa = dev.params_to_device(pa_np)
     pb = dev.params_to_device(block_params(np.random.default_rng(8), transition=True))
     gen = torch.Generator(device="cpu").manual_seed(11)
     z_full = torch.randn(n, n, 128, generator=gen).to(torch.bfloat16).cuda()
@@ -86,6 +90,17 @@ def main() -> int:
                                      where=ok_rows.cpu().numpy(), label=f"{grid.rows}x{grid.cols} {name} N={n}",
                                      mean_tol=1e-3)
                 print(info, flush=True)
+                if n <= 256 and not name.startswith("block"):
+                    # the CPU oracle's bf16 emulation of the reference, at the benchmark's tolerance
+                    x_np = z_full.float().cpu().numpy()[None]
+                    m_np = mask_full.cpu().numpy()[None]
+                    if name.startswith("trimul"):
+                        emu = orc.triangle_multiplication(pm_np, x_np, m_np, name.split()[1], dtype="bfloat16")[0]
+                    else:
+                        emu = orc.triangle_attention(pa_np, x_np, m_np, starting=name.endswith("starting"),
+                                                     dtype="bfloat16")[0]
+                    print(assert_parity(emu, full.float().cpu().numpy(), where=ok_rows.cpu().numpy(),
+                                        label=f"{grid.rows}x{grid.cols} {name} N={n} vs oracle"), flush=True)
             except AssertionError as exc:
                 failures += 1
                 print("FAILED", exc, flush=True)
@@ -97,6 +112,7 @@ def main() -> int:
         print("FAILED: repeated call differs", flush=True)
     flag = torch.tensor([failures], device="cuda")
     dist.all_reduce(flag)
+    ctx.close()
     dist.destroy_process_group()
     if ctx.rank == 0:
         print("CP_WORKER_OK" if flag.item() == 0 else "CP_WORKER_FAILED", flush=True)

@@ -54,7 +54,7 @@ def test_struct_sizes_match_the_header():
         pytest.skip("gcc not available")
     names = dict(_lib.STRUCTS)
     header = (ROOT / "include" / "b200tri.h").read_text()
-    assert set(re.findall(r"}\s*(b200tri_[a-z_]+_args);", header)) == set(names)
+    assert set(re.findall(r"}\s*(b200tri_[a-z_]+_(?:args|msg));", header)) == set(names)
     src = '#include <stdio.h>\n#include "b200tri.h"\nint main(void){\n'
     for cname in names:
         src += f'  printf("{cname} %zu\\n", sizeof({cname}));\n'

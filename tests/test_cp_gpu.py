@@ -22,11 +22,12 @@ def _run(world: int, tokens: int) -> str:
     env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(ROOT / "tests" / "cp_worker.py")]
-    done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900)
     assert done.returncode == 0 and "CP_WORKER_OK" in done.stdout, done.stdout[-3000:] + done.stderr[-3000:]
     return done.stdout
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (4, 512), (8, 1024)])
+@pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (2, 256), (4, 512), (4, 256), (8, 1024), (8, 256),
+                                          (8, 3072)])
 def test_context_parallel_matches_single_gpu(world, tokens):
     print(_run(world, tokens))

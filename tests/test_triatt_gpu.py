@@ -322,3 +322,64 @@ def test_attention_core_scale_argument_and_mixed_mask_bias(cuda_device):
     ref_nosoft = orc.attention_core(q_scaled, k, v, tb, np.where(soft[:, :, None, None, :], 0, np.maximum(mb5, -1e9)),
                                     dtype="bfloat16")
     assert orc.error_vs(ref_nosoft, got.float().cpu().numpy())["mean_abs_over_rms"] > 1e-2
+
+
+def test_core_walks_several_key_tiles_in_one_launch(cuda_device):
+    """b200tri_triatt_core_multi: one launch over key tiles that live in separate buffers
+    equals the one-shot core over the concatenated keys; and the context-parallel pattern -
+    own tile first (unnormalized), then every peer tile in one resumed launch - does too."""
+    from foldjax_b200 import _device as dev, _lib
+
+    lib = _lib.load()
+    g = torch.Generator(device="cpu").manual_seed(15)
+    n_i, n_j, h, d, n_kt, n_t = 5, 200, 4, 32, 128, 3
+    n_k = n_kt * n_t
+    q = (torch.randn(n_i, n_j, h * d, generator=g) * 0.6).bfloat16().to(cuda_device)
+    k = (torch.randn(n_i, n_k, h * d, generator=g) * 0.6).bfloat16().to(cuda_device)
+    v = torch.randn(n_i, n_k, h * d, generator=g).bfloat16().to(cuda_device)
+    bias = (torch.randn(h, n_j, n_k, generator=g) * 3.0 + torch.linspace(-5, 5, n_k)).bfloat16().to(cuda_device)
+    mask = (torch.rand(n_i, n_k, generator=g) > 0.2).float()
+    mask[:, 0] = 1.0
+    mask[n_i - 1, :n_kt] = 0.0
+    mask = mask.to(cuda_device)
+    keep = []  # buffers stay alive until the launches have run
+
+    def tile_args(sl, n_keys, **common):
+        vt = v[:, sl].transpose(1, 2).contiguous().half()
+        bd = bias[:, :, sl].contiguous()
+        kd = k[:, sl].contiguous()
+        md = mask[:, sl].contiguous()
+        keep.extend([vt, bd, kd, md])
+        return dict(n_i=n_i, n_j=n_j, n_k=n_keys, heads=h, head_dim=d, q=q.data_ptr(), k=kd.data_ptr(),
+                    vt=vt.data_ptr(), v_ld=n_keys, bias=bd.data_ptr(), bias_ld=n_keys, bias_head_stride=n_j * n_keys,
+                    mask=md.data_ptr(), ms_i=n_keys, ms_k=1, inf=1e9, **common)
+
+    def launch(arg_dicts):
+        n = len(arg_dicts)
+        nb = lib.b200tri_triatt_core_multi_workspace_bytes(n_i, arg_dicts[0]["n_k"], n)
+        ws = torch.empty(nb + 1024, dtype=torch.uint8, device=cuda_device)
+        keep.append(ws)
+        arr = (_lib.TriattCoreArgs * n)(*[
+            _lib.TriattCoreArgs(workspace=dev.aligned_ptr(ws), workspace_bytes=nb, **a) for a in arg_dicts])
+        _lib.check(lib.b200tri_triatt_core_multi(arr, n, C.c_void_p(dev.stream_ptr())))
+
+    ref = torch.empty(n_i, n_j, h * d, dtype=torch.bfloat16, device=cuda_device)
+    launch([tile_args(slice(0, n_k), n_k, o=ref.data_ptr())])
+    tiles = [slice(t * n_kt, (t + 1) * n_kt) for t in range(n_t)]
+    one = torch.full_like(ref, float("nan"))
+    launch([tile_args(sl, n_kt, o=one.data_ptr()) for sl in tiles])
+    acc = torch.zeros(n_i, n_j, h * d, dtype=torch.float32, device=cuda_device)
+    rmax = torch.zeros(n_i, h, n_j, dtype=torch.float32, device=cuda_device)
+    rsum = torch.zeros_like(rmax)
+    state = dict(row_max=rmax.data_ptr(), row_sum=rsum.data_ptr(), acc_o=acc.data_ptr())
+    two = torch.full_like(ref, float("nan"))
+    launch([tile_args(tiles[1], n_kt, o=two.data_ptr(), unnormalized=1, **state)])  # "own" tile first
+    launch([tile_args(sl, n_kt, o=two.data_ptr(), resume=1, **state) for sl in (tiles[2], tiles[0])])
+    torch.cuda.synchronize()
+    _lib.device_status()
+    r = ref.float().cpu().numpy()
+    print(assert_parity(r, one.float().cpu().numpy(), label="three key tiles, one launch", mean_tol=2e-4))
+    print(assert_parity(r, two.float().cpu().numpy(), label="own tile + resumed multi-tile launch", mean_tol=2e-4))
+    # too many tiles, or ragged tiles, are refused
+    bad = (_lib.TriattCoreArgs * 8)()
+    assert lib.b200tri_triatt_core_multi(bad, 8, None) == _lib.ERR_INVALID
