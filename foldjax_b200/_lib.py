@@ -181,6 +181,45 @@ class TriattCpArgs(C.Structure):
     ]
 
 
+class TrimulParams(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in ("norm_in_scale", "norm_in_bias", "p_in", "g_in", "norm_out_scale",
+                                          "norm_out_bias", "p_out", "g_out")]
+
+
+class TriattParams(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in ("norm_scale", "norm_bias", "w_bias", "w_q", "w_k", "w_v", "w_g", "w_o")]
+
+
+class TransitionParams(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in ("norm_scale", "norm_bias", "fc1", "fc2", "fc3")] + [("hidden", C.c_int32)]
+
+
+class AttentionParams(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in ("proj_q", "proj_q_bias", "proj_k", "proj_v", "proj_g", "proj_z_norm_scale",
+                                          "proj_z_norm_bias", "proj_z", "proj_o")]
+
+
+class PairformerBlockParams(C.Structure):
+    _fields_ = [
+        ("tri_mul_out", TrimulParams), ("tri_mul_in", TrimulParams),
+        ("tri_att_start", TriattParams), ("tri_att_end", TriattParams),
+        ("transition_z", TransitionParams),
+        ("pre_norm_s_scale", C.c_void_p), ("pre_norm_s_bias", C.c_void_p),
+        ("attention", AttentionParams), ("transition_s", TransitionParams),
+    ]
+
+
+class PairformerArgs(C.Structure):
+    _fields_ = [
+        ("n", C.c_int32), ("c_s", C.c_int32), ("heads_s", C.c_int32), ("n_blocks", C.c_int32), ("stacked", C.c_int32),
+        ("eps", C.c_float), ("tri_inf", C.c_float), ("att_inf", C.c_float),
+        ("params", C.POINTER(PairformerBlockParams)),
+        ("z_in", C.c_void_p), ("z_out", C.c_void_p), ("s_in", C.c_void_p), ("s_out", C.c_void_p),
+        ("pair_mask", C.c_void_p), ("mask", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 COMM_ID_BYTES = 128
 CP_TRIMUL_OUTGOING, CP_TRIMUL_INCOMING, CP_TRIATT_STARTING, CP_TRIATT_ENDING = range(4)
 
@@ -199,6 +238,15 @@ STRUCTS = {
     "b200tri_cp_msg": CpMsg,
     "b200tri_trimul_cp_args": TrimulCpArgs,
     "b200tri_triatt_cp_args": TriattCpArgs,
+    "b200tri_pairformer_args": PairformerArgs,
+}
+# parameter containers of the block-level call (checked the same way)
+PARAM_STRUCTS = {
+    "b200tri_trimul_params": TrimulParams,
+    "b200tri_triatt_params": TriattParams,
+    "b200tri_transition_params": TransitionParams,
+    "b200tri_attention_params": AttentionParams,
+    "b200tri_pairformer_block_params": PairformerBlockParams,
 }
 
 # name -> (restype, argtypes); every symbol include/b200tri.h declares.
@@ -246,6 +294,8 @@ SIGNATURES = {
     "b200tri_trimul_cp": (C.c_int, [C.c_void_p, C.POINTER(TrimulCpArgs), C.c_void_p]),
     "b200tri_triatt_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),
     "b200tri_triatt_cp": (C.c_int, [C.c_void_p, C.POINTER(TriattCpArgs), C.c_void_p]),
+    "b200tri_pairformer_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "b200tri_pairformer_forward": (C.c_int, [C.POINTER(PairformerArgs), C.c_void_p]),
     "b200tri_pair_transition_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_pair_transition": (C.c_int, [C.POINTER(PairTransitionArgs), C.c_void_p]),
     "b200tri_attention_pair_bias_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),

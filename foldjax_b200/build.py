@@ -78,5 +78,45 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+FFI_SRC = HERE.parent / "ffi" / "b200tri_ffi.cc"
+FFI_LIB = HERE / "libb200tri_ffi.so"
+
+
+def ffi_include_dir() -> Path | None:
+    """Directory holding xla/ffi/api/ffi.h (it ships inside jaxlib), or None."""
+    candidates = []
+    if os.environ.get("XLA_FFI_INCLUDE_DIR"):
+        candidates.append(Path(os.environ["XLA_FFI_INCLUDE_DIR"]))
+    try:
+        import jax.ffi  # noqa: PLC0415
+
+        candidates.append(Path(jax.ffi.include_dir()))
+    except Exception:
+        pass
+    for c in candidates:
+        if (c / "xla" / "ffi" / "api" / "ffi.h").exists():
+            return c
+    return None
+
+
+def build_ffi(verbose: bool = False) -> Path | None:
+    """Compile the XLA FFI handlers (ffi/b200tri_ffi.cc) against libb200tri.so when the XLA
+    FFI headers are available; returns None (and builds nothing) when they are not."""
+    inc = ffi_include_dir()
+    if inc is None:
+        if verbose:
+            sys.stderr.write("xla/ffi/api/ffi.h not found (no jaxlib here): libb200tri_ffi.so not built\n")
+        return None
+    build()
+    cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", str(inc),
+           "-I", str(HERE.parent / "include"), str(FFI_SRC), "-o", str(FFI_LIB),
+           f"-L{HERE}", "-l:libb200tri.so", "-Xlinker", "-rpath=$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the FFI handlers failed:\n{res.stdout}\n{res.stderr}")
+    return FFI_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_ffi(verbose=True) or "FFI handlers skipped")

@@ -77,6 +77,11 @@ size_t triatt_workspace_bytes_f32(int32_t n);
 int trimul_forward_f32(const b200tri_trimul_args* a, cudaStream_t stream);
 int triatt_forward_f32(const b200tri_triatt_args* a, cudaStream_t stream);
 
+// out[M][N] = (x * gate?) @ w (+ bias) (sigmoid?) (+ res): fp32 activations, bf16 weights [K][N]
+// (single_attention.cu; the single track's projections and transition use it).
+int launch_linear_f32(const float* x, const float* gate, const void* w, const void* bias, int M, int K, int N,
+                      int sigmoid, const float* res, float* out, cudaStream_t stream);
+
 // Launch accounting and optional per-kernel event timing.
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
                 K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_COUNT };

@@ -110,7 +110,8 @@ pair_bias_kernel(const __nv_bfloat16* __restrict__ z, long long n_pairs, int n, 
 // in front of the output projection). 64 x 64 tiles, 4 x 4 outputs per thread.
 __global__ void __launch_bounds__(256)
 linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ gate, const __nv_bfloat16* __restrict__ w,
-                  const __nv_bfloat16* __restrict__ b, int M, int K, int N, int sigmoid, float* __restrict__ out) {
+                  const __nv_bfloat16* __restrict__ b, int M, int K, int N, int sigmoid, float* __restrict__ out,
+                  const float* __restrict__ res = nullptr) {
   __shared__ float xs[16][64 + 1];
   __shared__ float ws[16][64];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -158,6 +159,7 @@ linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ gate, c
       if (nn >= N) continue;
       float v = acc[r][c] + (b ? __bfloat162float(b[nn]) : 0.f);
       if (sigmoid) v = 1.0f / (1.0f + expf(-v));
+      if (res) v += res[static_cast<long long>(m) * N + nn];
       out[static_cast<long long>(m) * N + nn] = v;
     }
   }
@@ -232,6 +234,17 @@ token_attention_kernel(const float* __restrict__ q, const float* __restrict__ k,
 }
 
 }  // namespace
+
+int launch_linear_f32(const float* x, const float* gate, const void* w, const void* bias, int M, int K, int N,
+                      int sigmoid, const float* res, float* out, cudaStream_t stream) {
+  const dim3 grid((N + 63) / 64, (M + 63) / 64);
+  count_launch();
+  linear_f32_kernel<<<grid, 256, 0, stream>>>(x, gate, static_cast<const __nv_bfloat16*>(w),
+                                              static_cast<const __nv_bfloat16*>(bias), M, K, N, sigmoid, out, res);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200TRI_OK;
+}
+
 }  // namespace b200
 
 extern "C" size_t b200tri_attention_pair_bias_workspace_bytes(int32_t n, int32_t c_s, int32_t heads) {

@@ -556,6 +556,57 @@ typedef struct {
 size_t b200tri_attention_pair_bias_workspace_bytes(int32_t n, int32_t c_s, int32_t heads);
 int b200tri_attention_pair_bias(const b200tri_attention_pair_bias_args* args, b200tri_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * One Pairformer block, or a stack of them (the trunk), as ONE call.
+ * Replaces: pairformer_layer_forward, src/foldjax/models/boltz2/models/trunk_blocks/
+ *   pairformer.py:100-206, and the lax.scan over stacked layer parameters around it
+ *   (pairformer.py:30-100, src/foldjax/models/_stacking.py).
+ * Per block:  z += tri_mul_out(z); z += tri_mul_in(z); z += tri_att_start(z);
+ *   z += tri_att_end(z); z += transition_z(z);
+ *   s += attention_pair_bias(LN(s), z, mask); s += transition_s(s).
+ * z is bf16 [n][n][128]; s is float32 [n][c_s] (the reference promotes the single track to
+ * float32, pairformer.py:182-206); every parameter is bf16 in the reference's layout.
+ * s_in = NULL runs the pair track only. z_out may alias z_in, s_out may alias s_in.
+ * `stacked` = 0: params points at n_blocks structs, one per block. `stacked` = 1: params
+ * points at ONE struct whose pointers are the bases of leaves stacked with a leading layer
+ * axis ([n_blocks, ...], what FoldJAX's scan carries); block l reads leaf l.
+ * --------------------------------------------------------------------- */
+typedef struct { const void *norm_in_scale, *norm_in_bias, *p_in, *g_in, *norm_out_scale, *norm_out_bias, *p_out, *g_out; } b200tri_trimul_params;
+typedef struct { const void *norm_scale, *norm_bias, *w_bias, *w_q, *w_k, *w_v, *w_g, *w_o; } b200tri_triatt_params;
+typedef struct { const void *norm_scale, *norm_bias, *fc1, *fc2, *fc3; int32_t hidden; } b200tri_transition_params;
+typedef struct { const void *proj_q, *proj_q_bias, *proj_k, *proj_v, *proj_g, *proj_z_norm_scale, *proj_z_norm_bias, *proj_z, *proj_o; } b200tri_attention_params;
+typedef struct {
+  b200tri_trimul_params tri_mul_out, tri_mul_in;
+  b200tri_triatt_params tri_att_start, tri_att_end;
+  b200tri_transition_params transition_z;   /* 128 -> hidden -> 128 (hidden 512) */
+  const void *pre_norm_s_scale, *pre_norm_s_bias; /* [c_s] */
+  b200tri_attention_params attention;       /* heads_s heads of width 24 */
+  b200tri_transition_params transition_s;   /* c_s -> hidden -> c_s */
+} b200tri_pairformer_block_params;
+
+typedef struct {
+  int32_t n;        /* tokens */
+  int32_t c_s;      /* 384 (0 with s_in = NULL) */
+  int32_t heads_s;  /* 16 */
+  int32_t n_blocks; /* 1 = one block, L = a trunk */
+  int32_t stacked;
+  float eps;        /* every layer norm (1e-5) */
+  float tri_inf;    /* triangle-attention mask constant (1e9) */
+  float att_inf;    /* single-track attention mask constant (1e6) */
+  const b200tri_pairformer_block_params* params;
+  const void* z_in;
+  void* z_out;
+  const float* s_in;
+  float* s_out;
+  const float* pair_mask; /* [n][n] or NULL (= ones) */
+  const float* mask;      /* [n] or NULL (= ones) */
+  void* workspace;        /* b200tri_pairformer_workspace_bytes, 1 KiB aligned */
+  size_t workspace_bytes;
+} b200tri_pairformer_args;
+
+size_t b200tri_pairformer_workspace_bytes(int32_t n, int32_t c_s, int32_t heads_s, int32_t hidden_z, int32_t hidden_s);
+int b200tri_pairformer_forward(const b200tri_pairformer_args* args, b200tri_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
