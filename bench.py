@@ -41,6 +41,12 @@ def block_flops(n: int) -> float:
     return 2.0 * (256.0 * n**3 + 196608.0 * n**2) + 2.0 * (512.0 * n**3 + 164864.0 * n**2)
 
 
+def single_track_flops(n: int, c_s: int = 384, heads: int = 16, c_z: int = 128) -> float:
+    """Single track of a block: five c_s x c_s projections, the 128 -> heads pair bias, the token
+    attention, and the c_s -> 4 c_s -> c_s transition."""
+    return (5 * 2.0 * n * c_s * c_s + 2.0 * n * n * c_z * heads + 4.0 * n * n * c_s + 3 * 2.0 * n * c_s * 4 * c_s)
+
+
 def make_params(rng: np.random.Generator) -> dict:
     from foldjax_b200.synthetic import block_params
 
@@ -83,6 +89,46 @@ def time_cpu(n: int, reps: int, warmup: int = 0) -> tuple[float, float]:
     return dt, block_flops(n) / dt / 1e12
 
 
+def time_cpu_config1() -> dict:
+    """BASELINE config 1 in full on the host cores: tri-mult outgoing then incoming, N = 256,
+    float32, all-ones mask, seed 0, through the NumPy restatement of the reference's jnp path."""
+    from oracle import triangle_oracle as orc
+
+    rng = np.random.default_rng(0)
+    n = 256
+    params = orc.random_trimul_params(rng)
+    x = rng.standard_normal((1, n, n, 128)).astype(np.float32)
+    mask = np.ones((1, n, n), np.float32)
+    t0 = time.perf_counter()
+    orc.triangle_multiplication(params, x, mask, "outgoing", dtype="float32")
+    orc.triangle_multiplication(params, x, mask, "incoming", dtype="float32")
+    dt = time.perf_counter() - t0
+    flops = 2.0 * (256.0 * n**3 + 196608.0 * n**2)
+    return {"config": "1: tri-mult out+in N=256 fp32", "seconds": dt, "tflops": flops / dt / 1e12,
+            "cores": len(os.sched_getaffinity(0))}
+
+
+def time_cpu_config3() -> dict:
+    """BASELINE config 3 in full on the host cores: one whole Pairformer block, N = 1024 with the
+    last 21 tokens padded, through the NumPy restatement (float32 arithmetic)."""
+    from oracle import triangle_oracle as orc
+
+    rng = np.random.default_rng(2)
+    n = 1024
+    params = orc.random_pairformer_params(rng)
+    z = rng.standard_normal((1, n, n, 128)).astype(np.float32)
+    sv = rng.standard_normal((1, n, 384)).astype(np.float32)
+    pair_mask = orc.pad_mask(n, 21)
+    mask = np.ones((1, n), np.float32)
+    mask[0, n - 21:] = 0.0
+    t0 = time.perf_counter()
+    orc.pairformer_layer(params, sv, z, mask, pair_mask, dtype="float32")
+    dt = time.perf_counter() - t0
+    flops = block_flops(n) + 2.0 * n * n * 3 * 128 * 512 + single_track_flops(n)
+    return {"config": "3: full Pairformer block N=1024 (21 padded)", "seconds": dt, "tflops": flops / dt / 1e12,
+            "cores": len(os.sched_getaffinity(0))}
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -94,13 +140,14 @@ def run_reference(args) -> None:
     line = {
         "impl": "reference",
         "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"pairformer-triangle-block N={args.tokens} c_z=128 4x32 heads (cfg 4 per block)",
                    "cpu_sample_tokens": n},
         "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference jnp path unavailable on this box (JAX not installed); NumPy restatement timed instead",
+        "cpu_configs_in_full": [time_cpu_config1()] + ([time_cpu_config3()] if args.cpu_config3 else []),
     }
     print(json.dumps(line), flush=True)
 
@@ -182,7 +229,26 @@ def run_gpu(args) -> None:
     n_pad = args.pad_tokens if args.pad_tokens >= 0 else (n - int(round(n * 3012 / 3072)) if n >= 64 else 0)
     mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
     mask = mask_host.cuda()
-    if world == 1:
+    s_dev = s_host = tok_mask = None
+    if args.full_block:
+        if world != 1:
+            raise SystemExit("--full-block runs on one GPU (the single track is not sharded)")
+        # the whole block through the one-call entry: pair track + pair transition + single track
+        from foldjax_b200.pairformer import pairformer_forward
+        from foldjax_b200.synthetic import pairformer_params
+
+        full = [dev.params_to_device(pairformer_params(rng)) for _ in range(args.blocks)]
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        s_dev = torch.randn(1, n, 384, device="cuda", generator=gen)
+        s_host = s_dev.cpu().pin_memory()
+        tok_mask = torch.ones(1, n, device="cuda")
+        if n_pad:
+            tok_mask[0, n - n_pad:] = 0.0
+        def run_block(zz, mm, ss=None):
+            return pairformer_forward(full, s_dev if ss is None else ss, zz, tok_mask, mm)[1]
+        grid_name = "single GPU, one library call per step"
+    elif world == 1:
         gen = torch.Generator(device="cuda").manual_seed(3)
         z = torch.randn(1, n, n, 128, device="cuda", generator=gen).to(torch.bfloat16)
         def run_block(zz, mm):
@@ -211,6 +277,14 @@ def run_gpu(args) -> None:
     out_host = torch.empty_like(z_host).pin_memory()
 
     def run_e2e():
+        if args.full_block:
+            zd, sd = z_host.cuda(non_blocking=True), s_host.cuda(non_blocking=True)
+            md = mask_host.cuda(non_blocking=True)
+            s_new, z_new = pairformer_forward(full, sd, zd, tok_mask, md)
+            out_host.copy_(z_new, non_blocking=True)
+            s_host.copy_(s_new, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return out_host
         if world == 1 and args.blocks == 1:
             return triangle_block_forward(params, z_host, mask_host, out=out_host)
         zd = z_host.cuda(non_blocking=True)
@@ -290,7 +364,9 @@ def run_gpu(args) -> None:
         return
 
     ms_step = ms_total / args.steps
-    flops = args.blocks * (block_flops(n) + (2.0 * n * n * 3 * 128 * 512 if args.transition else 0.0))
+    with_transition = args.transition or args.full_block
+    flops = args.blocks * (block_flops(n) + (2.0 * n * n * 3 * 128 * 512 if with_transition else 0.0)
+                           + (single_track_flops(n) if args.full_block else 0.0))
     peaks, peak_kind = measured_peaks()
     core_ms, core_n = ktimes["triatt_core"]
     core_avg = core_ms / max(core_n, 1)
@@ -304,28 +380,33 @@ def run_gpu(args) -> None:
     line = {
         "metric": METRIC, "value": flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {
-            "workload": f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
-                        "tri-mult out+in, tri-attn start+end, residual adds fused",
+            "workload": (f"pairformer-full-block N={n} c_z=128 c_s=384 (cfg 3 at N=1024/21 padded): tri-mult out+in, "
+                         "tri-attn start+end, pair transition, single attention with pair bias, single transition"
+                         if args.full_block else
+                         f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
+                         "tri-mult out+in, tri-attn start+end, residual adds fused"),
             "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops, "blocks_per_step": args.blocks,
-            "pair_transition_in_step": bool(args.transition),
+            "pair_transition_in_step": bool(with_transition), "single_track_in_step": bool(args.full_block),
             "parallelism": grid_name,
             "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
         },
         "clocks": clocks,
         "e2e": None if args.no_e2e else {
                 "value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(world * (z_host.numel() * 2 + mask_host.numel() * 4)),
-                "d2h_bytes_per_step": int(world * out_host.numel() * 2)},
+                "h2d_bytes_per_step": int(world * (z_host.numel() * 2 + mask_host.numel() * 4)
+                                          + (s_host.numel() * 4 if args.full_block else 0)),
+                "d2h_bytes_per_step": int(world * out_host.numel() * 2 + (s_host.numel() * 4 if args.full_block else 0))},
         "gpu_launches": launches,
         "roofline": {
             "kernel": "att_core_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"{peak_kind} sustained bf16",
-            # dram read + write bytes per launch from the committed ncu captures at N = 1024 and
-            # N = 3072 (profiles/att_core_n1024_ncu.md); not proportional to N, so null elsewhere
-            "traffic": {1024: 1.907e9, 3072: 5.55e10}.get(n) if world == 1 else None,
+            # dram read + write bytes per launch measured with ncu's DRAM counters at N = 1024 (this
+            # kernel) and N = 3072 (the same load pattern, one-off full-size capture); the traffic is
+            # not proportional to N (L2 hit rates change), so it is null at other sizes
+            "traffic": {1024: 1.93e9, 3072: 5.55e10}.get(n) if world == 1 else None,
             "avg_launch_ms": core_avg, "launches": core_n,
             "note": "binding resource is the MUFU/ALU softmax path (4*N^3 exps), not the tensor pipe",
         },
@@ -334,11 +415,16 @@ def run_gpu(args) -> None:
             "gbs": 3.0 * n * n * 256 / world / (transition_ms * 1e-3) / 1e9,
             "note": "LN + SwiGLU 128->512->128 + residual, one kernel; not part of `value`"},
         "kernel_ms_per_launch": {k: round(v[0] / max(v[1], 1), 4) for k, v in ktimes.items()},
+        # rank 0's timed kernels per step against the step: the rest is exchange that the tile compute
+        # did not hide, small untimed kernels and launch gaps
+        "kernel_ms_per_step": round(sum(v[0] for v in ktimes.values()) / args.steps, 4),
+        "non_kernel_ms_per_step": round(ms_step - sum(v[0] for v in ktimes.values()) / args.steps, 4),
         "kernel_time_share": shares,
         "cpu_baseline": None if cpu_tf is None else {
             "value": cpu_tf, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"one block's four triangle ops at N={args.cpu_tokens} fp32 via the NumPy restatement "
-                      f"({cpu_secs:.1f} s)"},
+                      f"({cpu_secs:.1f} s)",
+            "configs_in_full": [time_cpu_config1()] + ([time_cpu_config3()] if args.cpu_config3 else [])},
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -360,6 +446,11 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=384, help="size of the bounded CPU sample")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-config3", action="store_true",
+                    help="also time BASELINE config 3 (a whole block at N=1024) in full on the host cores (minutes)")
+    ap.add_argument("--full-block", action="store_true",
+                    help="one step = the WHOLE Pairformer block through the one-call entry: pair track with the pair "
+                         "transition, and the float32 single track (BASELINE config 3 with --tokens 1024 --pad-tokens 21)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -15,8 +15,11 @@
 // which costs the same bytes as reading a stored gate and saves writing one.
 //
 // V is stored transposed and in fp16: the core kernel multiplies P (fp16, 11
-// significand bits) by V on the tensor cores, and a bf16-rounded value is exactly
-// representable in fp16 (saturating beyond +-65504, flushing below 2^-24).
+// significand bits) by V on the tensor cores. A bf16-rounded value of magnitude in
+// [2^-14, 65504] is exactly representable in fp16 (8 significand bits fit in 11); larger
+// ones saturate, values in [2^-24, 2^-14) land on fp16 subnormals and lose significand
+// bits (at most the absolute 2^-25), smaller ones flush to zero. V is a layer-normed
+// projection of order one, so only the exact range matters in practice.
 //
 // One tile = 128 consecutive pairs (o, t0..t0+127). Persistent, one CTA per SM:
 //   warp 0      TMA producer (weights once, x tiles in a 3-stage ring)

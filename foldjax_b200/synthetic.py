@@ -48,6 +48,27 @@ def block_params(rng: np.random.Generator, transition: bool = False) -> dict:
     return params
 
 
+def attention_pair_bias_params(rng: np.random.Generator, c_s: int = 384, c_z: int = 128, heads: int = 16,
+                               std: float = 0.02) -> dict:
+    w = lambda *shape: (rng.standard_normal(shape) * std).astype(np.float32)
+    return {
+        "proj_q": {"kernel": w(c_s, c_s), "bias": w(c_s)}, "proj_k": {"kernel": w(c_s, c_s)},
+        "proj_v": {"kernel": w(c_s, c_s)}, "proj_g": {"kernel": w(c_s, c_s)},
+        "proj_z_norm": {"scale": np.ones(c_z, np.float32), "bias": np.zeros(c_z, np.float32)},
+        "proj_z": {"kernel": w(c_z, heads)}, "proj_o": {"kernel": w(c_s, c_s)},
+    }
+
+
+def pairformer_params(rng: np.random.Generator, c_s: int = 384, heads_s: int = 16) -> dict:
+    """Every sub-module of one Pairformer block, by the reference's names
+    (trunk_blocks/pairformer.py:126-206)."""
+    params = block_params(rng, transition=True)
+    params["pre_norm_s"] = {"scale": np.ones(c_s, np.float32), "bias": np.zeros(c_s, np.float32)}
+    params["attention"] = attention_pair_bias_params(rng, c_s=c_s, heads=heads_s)
+    params["transition_s"] = transition_params(rng, c_z=c_s)
+    return params
+
+
 def pad_mask(n: int, n_pad: int) -> np.ndarray:
     """[1, n, n] float32 pair mask m m^T with the last n_pad tokens dropped."""
     m = np.ones(n, dtype=np.float32)

@@ -437,6 +437,51 @@ def random_attention_pair_bias_params(rng: np.random.Generator, c_s: int = 384, 
     }
 
 
+# ------------------------------------------------------------- one Pairformer block
+def pairformer_layer(params: Params, s: np.ndarray | None, z: np.ndarray, mask: np.ndarray | None,
+                     pair_mask: np.ndarray | None, eps: float = 1e-5, dtype: str = "float64"):
+    """pairformer_layer_forward, trunk_blocks/pairformer.py:126-206: the four triangle updates
+    and the pair transition on z (trunk dtype, residual sums rounded to it), then the single
+    track in float32 (float64 here when ``dtype`` is "float64"): s += attention_pair_bias(LN(s),
+    z) ; s += transition_s(s). s = None runs the pair track only. Returns (s, z)."""
+    pr = _Prec(dtype)
+    z = pr.arr(z)
+    z = pr.r(z + triangle_multiplication(params["tri_mul_out"], z, pair_mask, "outgoing", eps, dtype))
+    z = pr.r(z + triangle_multiplication(params["tri_mul_in"], z, pair_mask, "incoming", eps, dtype))
+    z = pr.r(z + triangle_attention(params["tri_att_start"], z, pair_mask, True, eps=eps, dtype=dtype))
+    z = pr.r(z + triangle_attention(params["tri_att_end"], z, pair_mask, False, eps=eps, dtype=dtype))
+    z = pr.r(z + transition(params["transition_z"], z, eps, dtype))
+    if s is None:
+        return None, z
+    wide = "float64" if dtype == "float64" else "float32"
+    work = np.float64 if wide == "float64" else np.float32
+    s = np.asarray(s, dtype=work)
+    if mask is None:
+        mask = np.ones(s.shape[:2], dtype=work)
+    s_normed = layer_norm(s, params["pre_norm_s"]["scale"], params["pre_norm_s"]["bias"], eps, wide)
+    s = s + attention_pair_bias(params["attention"], s_normed, z, mask, k_in=s_normed, eps=eps, dtype=wide)
+    s = s + transition(params["transition_s"], s, eps, wide)
+    return s, z
+
+
+def random_pairformer_params(rng: np.random.Generator, c_s: int = 384, heads_s: int = 16, std: float = 0.02,
+                             ln_noise: float = 0.0) -> dict:
+    ln = lambda c: {"scale": (1.0 + ln_noise * rng.standard_normal(c)).astype(np.float32),
+                    "bias": (ln_noise * rng.standard_normal(c)).astype(np.float32)}
+    w = lambda *shape: (rng.standard_normal(shape) * std).astype(np.float32)
+    return {
+        "tri_mul_out": random_trimul_params(rng, std=std, ln_noise=ln_noise),
+        "tri_mul_in": random_trimul_params(rng, std=std, ln_noise=ln_noise),
+        "tri_att_start": random_triatt_params(rng, std=std, ln_noise=ln_noise),
+        "tri_att_end": random_triatt_params(rng, std=std, ln_noise=ln_noise),
+        "transition_z": random_transition_params(rng, std=std, ln_noise=ln_noise),
+        "pre_norm_s": ln(c_s),
+        "attention": random_attention_pair_bias_params(rng, c_s=c_s, heads=heads_s, std=std, ln_noise=ln_noise),
+        "transition_s": {"norm": ln(c_s), "fc1": {"kernel": w(c_s, 4 * c_s)}, "fc2": {"kernel": w(c_s, 4 * c_s)},
+                         "fc3": {"kernel": w(4 * c_s, c_s)}},
+    }
+
+
 # ------------------------------------------------------------ synthetic inputs
 def random_trimul_params(rng: np.random.Generator, c_z: int = 128, c_hidden: int = 128, std: float = 0.02,
                          ln_noise: float = 0.0) -> dict:
