@@ -38,6 +38,7 @@ class TrimulArgs(C.Structure):
         ("p_out", C.c_void_p), ("g_out", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("dtype", C.c_int32),
+        ("c_z", C.c_int32), ("c_hidden", C.c_int32),
     ]
 
 
@@ -90,7 +91,7 @@ class TriattArgs(C.Structure):
         ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p), ("w_bias", C.c_void_p),
         ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_g", C.c_void_p), ("w_o", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("dtype", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("dtype", C.c_int32), ("c_z", C.c_int32),
     ]
 
 
@@ -262,6 +263,8 @@ SIGNATURES = {
     "b200tri_timing_read": (C.c_int, [C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_int32)]),
     "b200tri_trimul_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_trimul_workspace_bytes_dtype": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "b200tri_trimul_workspace_bytes_shape": (C.c_size_t, [C.c_int32] * 4),
+    "b200tri_triatt_workspace_bytes_shape": (C.c_size_t, [C.c_int32] * 5),
     "b200tri_triatt_workspace_bytes_dtype": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200tri_trimul_forward": (C.c_int, [C.POINTER(TrimulArgs), C.c_void_p]),
     "b200tri_trimul_project_workspace_bytes": (C.c_size_t, []),

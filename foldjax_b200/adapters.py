@@ -109,3 +109,51 @@ def transition_params(norm: Any, fc1: Any, fc2: Any, fc3: Any) -> dict:
         "fc2": {"kernel": _kernel(fc2, "fc2")},
         "fc3": {"kernel": _kernel(fc3, "fc3")},
     }
+
+
+def esmfold2_triangle_multiplication_params(params: Any, prefix: str) -> dict:
+    """ESMFold2's flat checkpoint mapping -> the mapping ``triangle_multiplication_forward``
+    takes. ESMFold2 packs the four input projections into ONE linear, ``proj_bundle`` of
+    width 4c with torch ``[out, in]`` weights: rows [0, 2c) are the signal (left | right, our
+    a | b) and rows [2c, 4c) the gate logits (src/foldjax/models/esmfold2/models/trunk.py:52-62);
+    ``proj_emit`` / ``proj_gate`` are our ``p_out`` / ``g_out``, ``norm_start`` / ``norm_mix``
+    our ``norm_in`` / ``norm_out`` (:84-91). ``prefix`` names the
+    ``TriangleMultiplicativeUpdate``; the ``_engine`` level is added here as the reference does
+    (:45). Biases are optional in that checkpoint format; these projections carry none, and one
+    that does is refused rather than dropped."""
+    engine = f"{prefix}._engine" if prefix else "_engine"
+
+    def weight(name: str) -> Any:
+        if params.get(f"{engine}.{name}.bias") is not None:
+            raise ValueError(f"{engine}.{name}: linear biases are not supported by the b200 backend")
+        return params[f"{engine}.{name}.weight"]
+
+    bundle = weight("proj_bundle")  # [4c, c_z]
+    width = bundle.shape[0] // 2
+    return {
+        "norm_in": {"scale": params[f"{engine}.norm_start.weight"], "bias": params[f"{engine}.norm_start.bias"]},
+        "p_in": {"kernel": _t(bundle[:width])},
+        "g_in": {"kernel": _t(bundle[width:])},
+        "norm_out": {"scale": params[f"{engine}.norm_mix.weight"], "bias": params[f"{engine}.norm_mix.bias"]},
+        "p_out": {"kernel": _t(weight("proj_emit"))},
+        "g_out": {"kernel": _t(weight("proj_gate"))},
+    }
+
+
+def stack_layers(layers: list) -> Any:
+    """Per-layer parameter mappings -> ONE mapping whose leaves carry a leading layer axis,
+    the form the reference's scan carries (stack_leaves / prestack_layer_lists,
+    src/foldjax/models/_stacking.py:46-120) and ``pairformer_forward(..., num_blocks=L)`` takes.
+    A leaf that is None must be None in every layer."""
+    first = layers[0]
+    if isinstance(first, dict):
+        return {k: stack_layers([layer[k] for layer in layers]) for k in first}
+    if first is None:
+        if any(leaf is not None for leaf in layers):
+            raise ValueError("cannot stack mixed None/non-None layer leaves")
+        return None
+    if isinstance(first, np.ndarray) or np.isscalar(first):
+        return np.stack([np.asarray(leaf) for leaf in layers])
+    import torch
+
+    return torch.stack(list(layers))

@@ -71,11 +71,12 @@ int sm_count();
 // from several host threads (one per device under XLA).
 int ensure_smem_limit(const void* kernel, int bytes);
 
-// float32 mode of the two module-level entries (fp32_mode.cu).
-size_t trimul_workspace_bytes_f32(int32_t n);
-size_t triatt_workspace_bytes_f32(int32_t n);
-int trimul_forward_f32(const b200tri_trimul_args* a, cudaStream_t stream);
-int triatt_forward_f32(const b200tri_triatt_args* a, cudaStream_t stream);
+// The two module-level ops for every shape / element type outside the tensor-core
+// specialisation (generic.cu): other channel and head counts, float32 trunks.
+size_t trimul_workspace_bytes_generic(int32_t n, int32_t c_z, int32_t c_hidden, int32_t dtype);
+size_t triatt_workspace_bytes_generic(int32_t n, int32_t c_z, int32_t heads, int32_t head_dim);
+int trimul_forward_generic(const b200tri_trimul_args* a, int c_z, int c_hidden, cudaStream_t stream);
+int triatt_forward_generic(const b200tri_triatt_args* a, int c_z, cudaStream_t stream);
 
 // out[M][N] = (x * gate?) @ w (+ bias) (sigmoid?) (+ res): fp32 activations, bf16 weights [K][N]
 // (single_attention.cu; the single track's projections and transition use it).

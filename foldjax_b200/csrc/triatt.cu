@@ -42,9 +42,20 @@ extern "C" size_t b200tri_triatt_workspace_bytes(int32_t n) {
   return plan_offsets(n).total;
 }
 
+static bool specialised(int32_t dtype, int32_t c_z, int32_t heads, int32_t head_dim) {
+  return dtype == B200TRI_DTYPE_BF16 && c_z == 128 && heads == 4 && head_dim == 32;
+}
+
+extern "C" size_t b200tri_triatt_workspace_bytes_shape(int32_t n, int32_t dtype, int32_t c_z, int32_t heads,
+                                                       int32_t head_dim) {
+  c_z = c_z > 0 ? c_z : 128;
+  if (dtype != B200TRI_DTYPE_BF16 && dtype != B200TRI_DTYPE_F32) return 0;
+  if (specialised(dtype, c_z, heads, head_dim)) return b200tri_triatt_workspace_bytes(n);
+  return b200::triatt_workspace_bytes_generic(n, c_z, heads, head_dim);
+}
+
 extern "C" size_t b200tri_triatt_workspace_bytes_dtype(int32_t n, int32_t dtype) {
-  if (dtype == B200TRI_DTYPE_F32) return b200::triatt_workspace_bytes_f32(n);
-  return dtype == B200TRI_DTYPE_BF16 ? b200tri_triatt_workspace_bytes(n) : 0;
+  return b200tri_triatt_workspace_bytes_shape(n, dtype, 128, 4, 32);
 }
 
 extern "C" int b200tri_triatt_forward(const b200tri_triatt_args* a, b200tri_stream_t stream) {
@@ -52,19 +63,23 @@ extern "C" int b200tri_triatt_forward(const b200tri_triatt_args* a, b200tri_stre
   B200_REQUIRE(a != nullptr, B200TRI_ERR_INVALID, "triatt: null args");
   B200_REQUIRE(a->n > 0, B200TRI_ERR_INVALID, "triatt: n must be positive (got %d)", a->n);
   B200_REQUIRE(a->x && a->out, B200TRI_ERR_INVALID, "triatt: x/out must not be null");
-  B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
-               "triatt: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
   B200_REQUIRE(a->dtype == B200TRI_DTYPE_BF16 || a->dtype == B200TRI_DTYPE_F32, B200TRI_ERR_UNSUPPORTED,
                "triatt: unknown dtype %d", a->dtype);
-  if (a->dtype == B200TRI_DTYPE_F32) {
-    const size_t need = triatt_workspace_bytes_f32(a->n);
+  const int c_z = a->c_z > 0 ? a->c_z : 128;
+  B200_REQUIRE(a->heads >= 1 && a->heads <= 64 && a->head_dim >= 1, B200TRI_ERR_UNSUPPORTED,
+               "triatt: 1 to 64 heads (got %d x %d)", a->heads, a->head_dim);
+  B200_REQUIRE(c_z % 8 == 0 && c_z <= 1024, B200TRI_ERR_UNSUPPORTED,
+               "triatt: c_z must be a multiple of 8 up to 1024 (got %d)", c_z);
+  if (!specialised(a->dtype, c_z, a->heads, a->head_dim)) {
+    const size_t need = triatt_workspace_bytes_generic(a->n, c_z, a->heads, a->head_dim);
     B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
-                 "triatt (float32): workspace of %zu bytes needed for n=%d, got %zu", need, a->n, a->workspace_bytes);
+                 "triatt (general shapes): workspace of %zu bytes needed for n=%d, got %zu", need, a->n,
+                 a->workspace_bytes);
     B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
                  "triatt: workspace must be 1024-byte aligned");
     B200_REQUIRE(a->norm_scale && a->norm_bias && a->w_bias && a->w_q && a->w_k && a->w_v && a->w_g && a->w_o,
                  B200TRI_ERR_INVALID, "triatt: null parameter pointer");
-    return triatt_forward_f32(a, reinterpret_cast<cudaStream_t>(stream));
+    return triatt_forward_generic(a, c_z, reinterpret_cast<cudaStream_t>(stream));
   }
   const Plan pl = plan_offsets(a->n);
   B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,

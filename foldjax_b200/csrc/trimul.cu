@@ -50,9 +50,20 @@ extern "C" size_t b200tri_trimul_workspace_bytes(int32_t n) {
   return plan_offsets(n).total;
 }
 
+static bool specialised(int32_t dtype, int32_t c_z, int32_t c_hidden) {
+  return dtype == B200TRI_DTYPE_BF16 && c_z == 128 && c_hidden == 128;
+}
+
+extern "C" size_t b200tri_trimul_workspace_bytes_shape(int32_t n, int32_t dtype, int32_t c_z, int32_t c_hidden) {
+  c_z = c_z > 0 ? c_z : 128;
+  c_hidden = c_hidden > 0 ? c_hidden : 128;
+  if (dtype != B200TRI_DTYPE_BF16 && dtype != B200TRI_DTYPE_F32) return 0;
+  if (specialised(dtype, c_z, c_hidden)) return b200tri_trimul_workspace_bytes(n);
+  return b200::trimul_workspace_bytes_generic(n, c_z, c_hidden, dtype);
+}
+
 extern "C" size_t b200tri_trimul_workspace_bytes_dtype(int32_t n, int32_t dtype) {
-  if (dtype == B200TRI_DTYPE_F32) return b200::trimul_workspace_bytes_f32(n);
-  return dtype == B200TRI_DTYPE_BF16 ? b200tri_trimul_workspace_bytes(n) : 0;
+  return b200tri_trimul_workspace_bytes_shape(n, dtype, 128, 128);
 }
 
 extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stream_t stream) {
@@ -62,16 +73,20 @@ extern "C" int b200tri_trimul_forward(const b200tri_trimul_args* a, b200tri_stre
   B200_REQUIRE(a->x && a->out, B200TRI_ERR_INVALID, "trimul: x/out must not be null");
   B200_REQUIRE(a->dtype == B200TRI_DTYPE_BF16 || a->dtype == B200TRI_DTYPE_F32, B200TRI_ERR_UNSUPPORTED,
                "trimul: unknown dtype %d", a->dtype);
-  if (a->dtype == B200TRI_DTYPE_F32) {
-    const size_t need = trimul_workspace_bytes_f32(a->n);
+  const int c_z = a->c_z > 0 ? a->c_z : 128, c_hidden = a->c_hidden > 0 ? a->c_hidden : 128;
+  B200_REQUIRE(c_z % 8 == 0 && c_z <= 1024 && c_hidden % 8 == 0 && c_hidden <= 1024, B200TRI_ERR_UNSUPPORTED,
+               "trimul: channel counts must be multiples of 8 up to 1024 (got c_z %d, c_hidden %d)", c_z, c_hidden);
+  if (!specialised(a->dtype, c_z, c_hidden)) {
+    const size_t need = trimul_workspace_bytes_generic(a->n, c_z, c_hidden, a->dtype);
     B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need, B200TRI_ERR_WORKSPACE,
-                 "trimul (float32): workspace of %zu bytes needed for n=%d, got %zu", need, a->n, a->workspace_bytes);
+                 "trimul (general shapes): workspace of %zu bytes needed for n=%d, got %zu", need, a->n,
+                 a->workspace_bytes);
     B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
                  "trimul: workspace must be 1024-byte aligned");
     B200_REQUIRE(a->norm_in_scale && a->norm_in_bias && a->p_in && a->g_in && a->norm_out_scale && a->norm_out_bias &&
                      a->p_out && a->g_out,
                  B200TRI_ERR_INVALID, "trimul: null parameter pointer");
-    return trimul_forward_f32(a, reinterpret_cast<cudaStream_t>(stream));
+    return trimul_forward_generic(a, c_z, c_hidden, reinterpret_cast<cudaStream_t>(stream));
   }
   const Plan pl = plan_offsets(a->n);
   B200_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,

@@ -18,23 +18,27 @@ import torch
 from . import _device as dev
 from . import _lib
 
-C_Z = 128  # channel width the kernels are built for
+C_Z = 128  # channel width of the tensor-core specialisation (other widths run the general path)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def _check_pair(x: torch.Tensor) -> tuple[torch.Tensor, bool]:
-    squeeze = False
-    if x.dim() == 3:
-        x = x.unsqueeze(0)
-        squeeze = True
-    if x.dim() != 4 or x.shape[1] != x.shape[2]:
+def _check_pair(x: torch.Tensor) -> tuple[torch.Tensor, Any]:
+    """-> (the pair tensor as [B, N, N, C], the caller's leading shape). A missing batch axis is
+    added and leading axes beyond one are folded into B, the way the reference's fused
+    wrappers do it (src/foldjax/models/_cueq.py:89-121); the second item is what to restore."""
+    lead = tuple(x.shape[:-3])
+    if x.dim() < 3 or x.shape[-2] != x.shape[-3]:
         raise ValueError(f"expected a pair tensor [B, N, N, C], got shape {tuple(x.shape)}")
-    if x.shape[-1] != C_Z:
-        raise ValueError(f"libb200tri is built for c_z = {C_Z}; got {x.shape[-1]} channels")
-    return x, squeeze
+    if x.shape[-1] % 8 or x.shape[-1] > 1024:
+        raise ValueError(f"libb200tri takes channel counts that are multiples of 8 up to 1024; got {x.shape[-1]} channels")
+    return x.reshape((-1,) + tuple(x.shape[-3:])), lead
+
+
+def _unfold(t: torch.Tensor, lead: tuple) -> torch.Tensor:
+    return t.reshape(tuple(lead) + tuple(t.shape[1:]))
 
 
 def _leaf(params: Mapping, *path: str, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
@@ -99,15 +103,14 @@ def triangle_multiplication_forward(
     host_in = dev.is_host_array(x)
     numpy_in = isinstance(x, np.ndarray)
     tdt, code = resolve_dtype(x, dtype)
-    xd, squeeze = _check_pair(dev.to_device(x, tdt))
-    b, n = xd.shape[0], xd.shape[1]
+    xd, lead = _check_pair(dev.to_device(x, tdt))
+    b, n, c_z = xd.shape[0], xd.shape[1], xd.shape[3]
     md = None
     if mask is not None:
         md = dev.to_device(mask, torch.float32)
-        if md.dim() == 2:
-            md = md.unsqueeze(0)
-        if tuple(md.shape) != (b, n, n):
-            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
+        if md.dim() < 2 or tuple(md.shape[-2:]) != (n, n) or md.numel() != b * n * n:
+            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(x.shape)}")
+        md = md.reshape(b, n, n)
     rd = None
     if residual is not None:
         rd, _ = _check_pair(dev.to_device(residual, tdt))
@@ -115,8 +118,8 @@ def triangle_multiplication_forward(
     if out is None:
         out = torch.empty_like(xd)
     else:
-        if isinstance(out, torch.Tensor) and out.dim() == 3:
-            out = out.unsqueeze(0)
+        if isinstance(out, torch.Tensor) and out.numel() == xd.numel() and out.is_contiguous():
+            out = out.view(xd.shape) if tuple(out.shape[-3:]) == tuple(xd.shape[-3:]) else out
         dev.check_out(out, xd)
     leaves = {
         "norm_in_scale": _leaf(params, "norm_in", "scale", dtype=tdt),
@@ -128,20 +131,27 @@ def triangle_multiplication_forward(
         "p_out": _leaf(params, "p_out", "kernel", dtype=tdt),
         "g_out": _leaf(params, "g_out", "kernel", dtype=tdt),
     }
-    if tuple(leaves["p_in"].shape) != (C_Z, 2 * C_Z) or tuple(leaves["p_out"].shape) != (C_Z, C_Z):
-        raise ValueError("libb200tri is built for hidden width 128 (p_in [128,256], p_out [128,128])")
-    nbytes = lib.b200tri_trimul_workspace_bytes_dtype(n, code)
+    c_hidden = leaves["p_out"].shape[0]
+    want = {"norm_in_scale": (c_z,), "norm_in_bias": (c_z,), "p_in": (c_z, 2 * c_hidden), "g_in": (c_z, 2 * c_hidden),
+            "norm_out_scale": (c_hidden,), "norm_out_bias": (c_hidden,), "p_out": (c_hidden, c_z), "g_out": (c_z, c_z)}
+    for name, shape in want.items():
+        if tuple(leaves[name].shape) != shape:
+            raise ValueError(f"triangle multiplication parameter {name} has shape {tuple(leaves[name].shape)}, "
+                             f"expected {shape} for c_z = {c_z}, c_hidden = {c_hidden}")
+    if c_hidden % 8 or c_hidden > 1024:
+        raise ValueError(f"libb200tri takes hidden widths that are multiples of 8 up to 1024; got {c_hidden}")
+    nbytes = lib.b200tri_trimul_workspace_bytes_shape(n, code, c_z, c_hidden)
     ws = dev.workspace(nbytes, "trimul")
     for bi in range(b):
         args = _lib.TrimulArgs(
             n=n, incoming=int(direction == "incoming"), eps=float(eps),
             x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
             residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
-            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code,
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code, c_z=c_z, c_hidden=c_hidden,
             **{k: v.data_ptr() for k, v in leaves.items()},
         )
         _lib.check(lib.b200tri_trimul_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))
-    result = out[0] if squeeze else out
+    result = _unfold(out, lead)
     if host_in:
         host = result.float().cpu() if numpy_in else result.cpu()
         dev.check_device_status()  # the copy synchronised: a kernel that gave up on a wait shows here

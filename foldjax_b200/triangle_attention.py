@@ -18,7 +18,7 @@ import torch
 
 from . import _device as dev
 from . import _lib
-from .triangle import C_Z, _check_pair, _leaf, _ptr, resolve_dtype
+from .triangle import C_Z, _check_pair, _leaf, _ptr, _unfold, resolve_dtype
 
 HEADS = 4
 HEAD_DIM = 32
@@ -59,15 +59,14 @@ def triangle_attention_forward(
     host_in = dev.is_host_array(x)
     numpy_in = isinstance(x, np.ndarray)
     tdt, code = resolve_dtype(x, dtype)
-    xd, squeeze = _check_pair(dev.to_device(x, tdt))
-    b, n = xd.shape[0], xd.shape[1]
+    xd, lead = _check_pair(dev.to_device(x, tdt))
+    b, n, c_z = xd.shape[0], xd.shape[1], xd.shape[3]
     md = None
     if mask is not None:
         md = dev.to_device(mask, torch.float32)
-        if md.dim() == 2:
-            md = md.unsqueeze(0)
-        if tuple(md.shape) != (b, n, n):
-            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(xd.shape)}")
+        if md.dim() < 2 or tuple(md.shape[-2:]) != (n, n) or md.numel() != b * n * n:
+            raise ValueError(f"mask shape {tuple(md.shape)} does not match pair tensor {tuple(x.shape)}")
+        md = md.reshape(b, n, n)
     rd = None
     if residual is not None:
         rd, _ = _check_pair(dev.to_device(residual, tdt))
@@ -75,8 +74,8 @@ def triangle_attention_forward(
     if out is None:
         out = torch.empty_like(xd)
     else:
-        if isinstance(out, torch.Tensor) and out.dim() == 3:
-            out = out.unsqueeze(0)
+        if isinstance(out, torch.Tensor) and out.numel() == xd.numel() and out.is_contiguous():
+            out = out.view(xd.shape) if tuple(out.shape[-3:]) == tuple(xd.shape[-3:]) else out
         dev.check_out(out, xd)
     leaves = {
         "norm_scale": _leaf(params, "layer_norm", "scale", dtype=tdt),
@@ -88,20 +87,29 @@ def triangle_attention_forward(
         "w_g": _leaf(params, "mha", "linear_g", "kernel", dtype=tdt),
         "w_o": _leaf(params, "mha", "linear_o", "kernel", dtype=tdt),
     }
-    if tuple(leaves["w_bias"].shape) != (C_Z, HEADS) or tuple(leaves["w_q"].shape) != (C_Z, HEADS * HEAD_DIM):
-        raise ValueError("libb200tri is built for 4 heads x 32 (linear [128,4], linear_q [128,128])")
-    nbytes = lib.b200tri_triatt_workspace_bytes_dtype(n, code)
+    heads = leaves["w_bias"].shape[-1]
+    width = leaves["w_g"].shape[-1]
+    head_dim = width // max(heads, 1)
+    want = {"norm_scale": (c_z,), "norm_bias": (c_z,), "w_bias": (c_z, heads), "w_q": (c_z, width), "w_k": (c_z, width),
+            "w_v": (c_z, width), "w_g": (c_z, width), "w_o": (width, c_z)}
+    for name, shape in want.items():
+        if tuple(leaves[name].shape) != shape:
+            raise ValueError(f"triangle attention parameter {name} has shape {tuple(leaves[name].shape)}, expected "
+                             f"{shape} for c_z = {c_z}, {heads} heads x {head_dim}")
+    if heads * head_dim != width or head_dim not in (8, 16, 24, 32, 48, 64):
+        raise ValueError(f"libb200tri takes head widths 8, 16, 24, 32, 48 and 64; got {heads} heads over {width} channels")
+    nbytes = lib.b200tri_triatt_workspace_bytes_shape(n, code, c_z, heads, head_dim)
     ws = dev.workspace(nbytes, "triatt")
     for bi in range(b):
         args = _lib.TriattArgs(
-            n=n, starting=int(bool(starting)), heads=HEADS, head_dim=HEAD_DIM, inf=float(inf), eps=float(eps),
+            n=n, starting=int(bool(starting)), heads=heads, head_dim=head_dim, inf=float(inf), eps=float(eps),
             x=xd[bi].data_ptr(), mask=_ptr(md[bi]) if md is not None else None,
             residual=_ptr(rd[bi]) if rd is not None else None, out=out[bi].data_ptr(),
-            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code,
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, dtype=code, c_z=c_z,
             **{k: v.data_ptr() for k, v in leaves.items()},
         )
         _lib.check(lib.b200tri_triatt_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))
-    result = out[0] if squeeze else out
+    result = _unfold(out, lead)
     if host_in:
         host = result.float().cpu() if numpy_in else result.cpu()
         dev.check_device_status()  # the copy synchronised: a kernel that gave up on a wait shows here

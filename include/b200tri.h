@@ -114,10 +114,17 @@ typedef struct {
   size_t workspace_bytes;
   int32_t dtype; /* B200TRI_DTYPE_*: type of x, mask excepted (always float32), of every
                     parameter, of residual and of out. 0 = bf16. */
+  /* Channel counts, 0 = 128: x is [n, n, c_z]; p_in / g_in [c_z, 2 * c_hidden]; norm_out
+   * [c_hidden]; p_out [c_hidden, c_z]; g_out [c_z, c_z]. c_z = c_hidden = 128 in bf16 runs the
+   * tensor-core kernels end to end; any other shape (the template stacks' c_z = 64 with
+   * c_hidden = 128, the 384-channel refiner) or float32 runs the general path: CUDA-core
+   * stages around the tensor-core contraction. Multiples of 8, up to 1024. */
+  int32_t c_z, c_hidden;
 } b200tri_trimul_args;
 
-size_t b200tri_trimul_workspace_bytes(int32_t n); /* bf16 */
-size_t b200tri_trimul_workspace_bytes_dtype(int32_t n, int32_t dtype);
+size_t b200tri_trimul_workspace_bytes(int32_t n); /* bf16, 128 channels */
+size_t b200tri_trimul_workspace_bytes_dtype(int32_t n, int32_t dtype); /* 128 channels */
+size_t b200tri_trimul_workspace_bytes_shape(int32_t n, int32_t dtype, int32_t c_z, int32_t c_hidden);
 int b200tri_trimul_forward(const b200tri_trimul_args* args, b200tri_stream_t stream);
 
 /* The three stages of the update, exposed so that the 2-D context-parallel
@@ -216,7 +223,7 @@ int b200tri_trimul_finish(const b200tri_trimul_finish_args* args, b200tri_stream
  *   cueq_attention_core (src/foldjax/models/_cueq.py:66-121).
  * Parameters in the reference's layout: layer_norm scale/bias [128]; `linear`
  * (pair bias) [128, 4]; linear_q/k/v/g [128, 128] with heads-major columns;
- * linear_o [128, 128]. starting = 0 computes the ending node: the same
+ * linear_o [128, 128] (other shapes: see c_z below). starting = 0 computes the ending node: the same
  * attention on the transposed pair tensor and mask, result transposed back.
  * If `residual` is not NULL the kernel writes residual + update.
  * --------------------------------------------------------------------- */
@@ -242,10 +249,16 @@ typedef struct {
   void* workspace;
   size_t workspace_bytes;
   int32_t dtype; /* B200TRI_DTYPE_*, as in b200tri_trimul_args */
+  /* 0 = 128. x is [n, n, c_z]; linear (w_bias) [c_z, heads]; linear_q/k/v/g [c_z, heads *
+   * head_dim]; linear_o [heads * head_dim, c_z]. bf16 with c_z = 128 and 4 heads x 32 runs the
+   * tensor-core kernels; other shapes (head widths 8, 16, 24, 32, 48, 64) or float32 run the
+   * general CUDA-core path. */
+  int32_t c_z;
 } b200tri_triatt_args;
 
-size_t b200tri_triatt_workspace_bytes(int32_t n); /* bf16 */
+size_t b200tri_triatt_workspace_bytes(int32_t n); /* bf16, c_z = 128, 4 heads x 32 */
 size_t b200tri_triatt_workspace_bytes_dtype(int32_t n, int32_t dtype);
+size_t b200tri_triatt_workspace_bytes_shape(int32_t n, int32_t dtype, int32_t c_z, int32_t heads, int32_t head_dim);
 int b200tri_triatt_forward(const b200tri_triatt_args* args, b200tri_stream_t stream);
 
 /* Stages, exposed for the context-parallel ring (the reference's

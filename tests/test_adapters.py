@@ -176,3 +176,59 @@ def test_transition_adapter_matches_torch_layout_formula():
     expected = _lin(a * _sig(a) * _lin(xn, fc2), fc3)
     got = orc.transition(adapters.transition_params(norm, fc1, fc2, fc3), x, dtype="float64")
     np.testing.assert_allclose(got, expected, rtol=1e-9, atol=1e-9)
+
+
+def test_esmfold2_packed_bundle_maps_to_the_fused_projections():
+    """ESMFold2's formula (trunk.py:45-91: one `proj_bundle` linear, signal * sigmoid(gate),
+    left | right halves) restated here on its own flat parameter names, against the oracle run
+    on the adapted mapping."""
+    from foldjax_b200 import adapters
+    from oracle import triangle_oracle as orc
+
+    rng = np.random.default_rng(41)
+    n, c_z, c = 9, 128, 128
+    prefix = "trunk.blocks.0.tri_out"
+    e = prefix + "._engine"
+    flat = {
+        f"{e}.norm_start.weight": 1 + 0.1 * rng.standard_normal(c_z), f"{e}.norm_start.bias": 0.1 * rng.standard_normal(c_z),
+        f"{e}.proj_bundle.weight": 0.1 * rng.standard_normal((4 * c, c_z)),
+        f"{e}.norm_mix.weight": 1 + 0.1 * rng.standard_normal(c), f"{e}.norm_mix.bias": 0.1 * rng.standard_normal(c),
+        f"{e}.proj_emit.weight": 0.1 * rng.standard_normal((c_z, c)),
+        f"{e}.proj_gate.weight": 0.1 * rng.standard_normal((c_z, c_z)),
+    }
+    x = rng.standard_normal((1, n, n, c_z))
+    mask = (rng.random((1, n, n)) > 0.2).astype(np.float64)
+
+    def ln(v, w, b):
+        mu = v.mean(-1, keepdims=True)
+        var = ((v - mu) ** 2).mean(-1, keepdims=True)
+        return (v - mu) / np.sqrt(var + 1e-5) * w + b
+
+    sig = lambda v: 1 / (1 + np.exp(-v))
+    for outgoing in (True, False):
+        normed = ln(x, flat[f"{e}.norm_start.weight"], flat[f"{e}.norm_start.bias"])
+        bundled = normed @ flat[f"{e}.proj_bundle.weight"].T
+        width = bundled.shape[-1] // 2
+        routed = bundled[..., :width] * sig(bundled[..., width:]) * mask[..., None]
+        left, right = routed[..., : width // 2], routed[..., width // 2:]
+        contracted = np.einsum("bikd,bjkd->bijd" if outgoing else "bkid,bkjd->bijd", left, right)
+        mixed = ln(contracted, flat[f"{e}.norm_mix.weight"], flat[f"{e}.norm_mix.bias"]) @ flat[f"{e}.proj_emit.weight"].T
+        want = mixed * sig(normed @ flat[f"{e}.proj_gate.weight"].T)
+        mapped = adapters.esmfold2_triangle_multiplication_params(flat, prefix)
+        got = orc.triangle_multiplication(mapped, x, mask, "outgoing" if outgoing else "incoming", dtype="float64")
+        np.testing.assert_allclose(got, want, rtol=1e-9, atol=1e-11)
+    flat[f"{e}.proj_gate.bias"] = np.zeros(c_z)
+    with pytest.raises(ValueError, match="biases are not supported"):
+        adapters.esmfold2_triangle_multiplication_params(flat, prefix)
+
+
+def test_stack_layers_builds_the_scan_form():
+    from foldjax_b200 import adapters
+
+    layers = [{"a": {"w": np.full((2, 3), i, np.float32)}, "n": 4, "none": None} for i in range(3)]
+    stacked = adapters.stack_layers(layers)
+    assert stacked["a"]["w"].shape == (3, 2, 3) and stacked["a"]["w"][2, 0, 0] == 2
+    assert stacked["n"].tolist() == [4, 4, 4] and stacked["none"] is None
+    layers[1]["none"] = 1
+    with pytest.raises(ValueError, match="mixed None"):
+        adapters.stack_layers(layers)

@@ -170,8 +170,10 @@ def test_bad_arguments_are_rejected(cuda_device):
     x = np.zeros((1, 8, 8, 128), np.float32)
     with pytest.raises(ValueError, match="Unsupported triangle multiplication direction"):
         triangle_multiplication_forward(params, x, None, "sideways")
-    with pytest.raises(ValueError, match="c_z = 128"):
+    with pytest.raises(ValueError, match="expected \\(64,\\)"):  # 64-channel input, 128-channel parameters
         triangle_multiplication_forward(params, np.zeros((1, 8, 8, 64), np.float32), None, "outgoing")
+    with pytest.raises(ValueError, match="multiples of 8"):
+        triangle_multiplication_forward(params, np.zeros((1, 8, 8, 60), np.float32), None, "outgoing")
     lib = _lib.load()
     args = _lib.TrimulArgs(n=8)
     assert lib.b200tri_trimul_forward(C.byref(args), None) == _lib.ERR_INVALID
