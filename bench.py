@@ -374,6 +374,7 @@ def run_gpu(args) -> None:
     core_flops_rank = 2.0 * 4.0 * n**3 * 128.0 / world * args.steps * args.blocks
     achieved = core_flops_rank / (core_ms * 1e-3) / 1e12 if core_ms else None
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
+    exchange_ms, exchange_n = ktimes.pop("cp_exchange", (0.0, 0))  # a span on the exchange stream, not a kernel
     shares = {k: round(v[0] / max(sum(t[0] for t in ktimes.values()), 1e-9), 4) for k, v in ktimes.items()}
     cores = len(os.sched_getaffinity(0))
     cpu_secs, cpu_tf = time_cpu(args.cpu_tokens, reps=1) if world == 1 and not args.no_cpu else (None, None)
@@ -419,6 +420,10 @@ def run_gpu(args) -> None:
         # did not hide, small untimed kernels and launch gaps
         "kernel_ms_per_step": round(sum(v[0] for v in ktimes.values()) / args.steps, 4),
         "non_kernel_ms_per_step": round(ms_step - sum(v[0] for v in ktimes.values()) / args.steps, 4),
+        # context-parallel runs: time the send/receive groups spent on the exchange stream per step
+        # (transfer time plus waiting for the peers; part of it overlaps the attention core)
+        "cp_exchange_ms_per_step": round(exchange_ms / args.steps, 4) if world > 1 else None,
+        "cp_exchange_groups_per_step": exchange_n // max(args.steps, 1) if world > 1 else None,
         "kernel_time_share": shares,
         "cpu_baseline": None if cpu_tf is None else {
             "value": cpu_tf, "unit": UNIT, "cores": cores, "kind": "port",

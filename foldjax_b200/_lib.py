@@ -343,7 +343,7 @@ def device_status() -> int:
 
 
 KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish",
-           "pair_transition", "pair_bias")
+           "pair_transition", "pair_bias", "cp_exchange")
 
 
 def kernel_times() -> dict[str, tuple[float, int]]:

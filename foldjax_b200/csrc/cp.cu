@@ -170,6 +170,9 @@ int post_exchange(b200tri_comm* cm, const std::vector<Msg>& msgs, Want want, Vie
   B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
   std::vector<Piece> send, recv;
   bool grouped = false;
+  // with timing on, the span of this group on the exchange stream (it starts when the stream
+  // has seen the caller's "tiles are ready" event, so it is transfer time plus peer skew)
+  TimedLaunch timed(K_CP_EXCHANGE, cm->stream);
   for (const Msg& msg : msgs) {
     if (!want(msg) || (msg.src != cm->rank && msg.dst != cm->rank)) continue;
     send.clear();

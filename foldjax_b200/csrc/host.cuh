@@ -85,7 +85,7 @@ int launch_linear_f32(const float* x, const float* gate, const void* w, const vo
 
 // Launch accounting and optional per-kernel event timing.
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
-                K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_COUNT };
+                K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_CP_EXCHANGE, K_COUNT };
 void count_launch(int n = 1);
 bool timing_enabled();
 struct TimedLaunch {  // brackets the launches made during its lifetime

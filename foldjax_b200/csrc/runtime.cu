@@ -92,7 +92,7 @@ static std::mutex g_timing_mu;
 static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events[K_COUNT];
 static const char* const kKernelNames[K_COUNT] = {"trimul_project", "trimul_contract", "trimul_finish",
                                                   "triatt_project", "triatt_core",     "triatt_finish",
-                                                  "pair_transition", "pair_bias"};
+                                                  "pair_transition", "pair_bias",      "cp_exchange"};
 
 bool timing_enabled() { return g_timing[current_device_slot()].load(std::memory_order_relaxed) != 0; }
 

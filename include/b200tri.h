@@ -68,7 +68,8 @@ int b200tri_selftest_wait(int64_t limit_cycles, b200tri_stream_t stream);
  *   kernels with CUDA events on the launching stream. b200tri_timing_read
  *   synchronises the device and returns, for a kernel name ("trimul_project",
  *   "trimul_contract", "trimul_finish", "triatt_project", "triatt_core",
- *   "triatt_finish", "pair_transition", "pair_bias"), the summed duration in ms and the number of launches since
+ *   "triatt_finish", "pair_transition", "pair_bias"; "cp_exchange" = the send/receive groups of the
+ *   context-parallel ops, timed on the exchange stream), the summed duration in ms and the number of launches since
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
 /* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
