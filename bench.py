@@ -67,8 +67,11 @@ def cpu_block(params, z, mask, dtype="float32"):
 
     z = z + orc.triangle_multiplication(params["tri_mul_out"], z, mask, "outgoing", dtype=dtype)
     z = z + orc.triangle_multiplication(params["tri_mul_in"], z, mask, "incoming", dtype=dtype)
-    z = z + orc.triangle_attention(params["tri_att_start"], z, mask, starting=True, dtype=dtype)
-    z = z + orc.triangle_attention(params["tri_att_end"], z, mask, starting=False, dtype=dtype)
+    # attention rows are independent: chunks of rows run on half of the cores, the other half is
+    # left to the BLAS threads inside each chunk (one chunk per core oversubscribes and is slower)
+    threads = max(1, len(os.sched_getaffinity(0)) // 2)
+    z = z + orc.triangle_attention(params["tri_att_start"], z, mask, starting=True, dtype=dtype, threads=threads)
+    z = z + orc.triangle_attention(params["tri_att_end"], z, mask, starting=False, dtype=dtype, threads=threads)
     return z
 
 

@@ -150,6 +150,25 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// Tiled TMA store, shared memory -> global (bulk async-group completion). The tile must have
+// been written with ordinary shared-memory stores followed by fence_proxy_async() and a
+// barrier; elements outside the tensor are not written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
+               "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(m),
+               "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the stores committed so far have READ their shared-memory source (it may be reused).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Until the stores committed so far are complete (written and visible).
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_in_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_in_smem)),
@@ -338,6 +357,25 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
 // Named barrier among `nthreads` threads (id 1..15; 0 is __syncthreads()).
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// The same barrier with an AND-reduction of a predicate: every thread learns whether ALL of
+// them passed `ok`. Used after a bounded wait whose result must be acted on by a whole group
+// that later meets at a named barrier: if one thread gave up and left while the others
+// proceeded, the next barrier would never complete.
+__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads, bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      " .reg .pred p, q;\n"
+      " setp.ne.u32 q, %3, 0;\n"
+      " bar.red.and.pred p, %1, %2, q;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return out != 0;
 }
 
 }  // namespace b200

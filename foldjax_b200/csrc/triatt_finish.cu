@@ -30,11 +30,21 @@ namespace {
 constexpr int STAGES = 2;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
 constexpr int THREADS = 320;
+constexpr int EPI_THREAD0 = 192;  // first thread of the epilogue warps
+// 1: the epilogue stages the output tile in shared memory ([128 pairs][128 channels] as two
+// swizzled slabs) and writes it with two TMA stores through the caller's strides; 0: every
+// thread stores its pair's row itself, 64 bytes at a time (32 cache lines per warp store).
+#ifndef B200_AFIN_TMASTORE
+#define B200_AFIN_TMASTORE 1
+#endif
 
 struct Smem {
   uint8_t w[4 * SLAB_BYTES];  // Wg^T (2 slabs), Wo^T (2 slabs)
   uint8_t x[STAGES][TILE_BYTES];
   uint8_t o[STAGES][TILE_BYTES];
+#if B200_AFIN_TMASTORE
+  uint8_t out[TILE_BYTES];
+#endif
   uint32_t gamma2[64], beta2[64];
   uint64_t w_full, in_full[STAGES], xn_full[STAGES], y_full[STAGES], in_empty[STAGES];
   uint64_t g_full[2], g_empty[2], out_full[2], out_empty[2];
@@ -55,7 +65,8 @@ struct Params {
 
 __global__ void __launch_bounds__(THREADS, 1)
 att_finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
-                  const __grid_constant__ CUtensorMap tm_w, const Params p) {
+                  const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out,
+                  const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
@@ -227,7 +238,14 @@ att_finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       const int o = static_cast<int>(tile / p.tiles_inner);
       const int t = static_cast<int>(tile % p.tiles_inner) * 128 + row;
       const uint32_t a = it & 1, aph = (it >> 1) & 1;
+#if B200_AFIN_TMASTORE
+      // the previous tile must have left the staging buffer; the vote makes the outcome of the
+      // bounded wait the same for all 128 threads, which meet at a barrier below
+      if (threadIdx.x == EPI_THREAD0) tma_store_wait_read();
+      if (!named_barrier_and(1, 128, mbar_wait(&sm.out_full[a], aph, p.status, ST_TIMEOUT_EPILOGUE))) break;
+#else
       if (!mbar_wait(&sm.out_full[a], aph, p.status, ST_TIMEOUT_EPILOGUE)) break;
+#endif
       tc_fence_after();
       const long long off = static_cast<long long>(o) * p.os_outer + static_cast<long long>(t) * p.os_inner;
 #pragma unroll 1
@@ -236,7 +254,9 @@ att_finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tmem_ld32(lane_addr + a * 256 + 128 + chunk * 32, v);
         tmem_ld_wait();
         if (t < p.n_inner) {
+#if !B200_AFIN_TMASTORE
           uint4* dst = reinterpret_cast<uint4*>(p.out + off + chunk * 32);
+#endif
           const uint4* res = p.residual ? reinterpret_cast<const uint4*>(p.residual + off + chunk * 32) : nullptr;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -251,16 +271,34 @@ att_finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
               u[2] = bf16x2_add(rv.z, u[2]);
               u[3] = bf16x2_add(rv.w, u[3]);
             }
+#if B200_AFIN_TMASTORE
+            *reinterpret_cast<uint4*>(sm.out + (chunk >> 1) * SLAB_BYTES + sw128_offset(row, (chunk & 1) * 4 + q)) =
+                make_uint4(u[0], u[1], u[2], u[3]);
+#else
             dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+#endif
           }
         }
       }
+#if B200_AFIN_TMASTORE
+      fence_proxy_async();
+      named_barrier(1, 128);
+      if (threadIdx.x == EPI_THREAD0) {  // rows past n_inner are outside the tensor and are not written
+        const int t0 = static_cast<int>(tile % p.tiles_inner) * 128;
+        tma_store_3d(&tm_out, sm.out, 0, t0, o);
+        tma_store_3d(&tm_out, sm.out + SLAB_BYTES, 64, t0, o);
+        tma_store_commit();
+      }
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.out_empty[a]);
     }
   }
 
+#if B200_AFIN_TMASTORE
+  if (threadIdx.x == EPI_THREAD0) tma_store_wait_all();
+#endif
   if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);
   tc_fence_before();
@@ -297,7 +335,14 @@ extern "C" int b200tri_triatt_finish(const b200tri_triatt_finish_args* a, b200tr
   pack_copy_words(a->norm_scale, ln, 64, stream);
   pack_copy_words(a->norm_bias, ln + 64, 64, stream);
 
-  CUtensorMap tm_x, tm_o, tm_w;
+  CUtensorMap tm_x, tm_o, tm_w, tm_out;
+  {  // the result through the caller's strides (the ending node lands transposed back in place)
+    const uint64_t dims[3] = {128, (uint64_t)a->n_inner, (uint64_t)a->n_outer};
+    const uint64_t str[2] = {(uint64_t)a->os_inner * 2, (uint64_t)a->os_outer * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = make_tmap(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
   {
     const uint64_t dims[3] = {128, (uint64_t)a->n_inner, (uint64_t)a->n_outer};
     const uint64_t str[2] = {(uint64_t)a->xs_inner * 2, (uint64_t)a->xs_outer * 2};
@@ -340,7 +385,7 @@ extern "C" int b200tri_triatt_finish(const b200tri_triatt_finish_args* a, b200tr
   {
     TimedLaunch timed(K_TRIATT_FINISH, stream);
     count_launch();
-    att_finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_o, tm_w, p);
+    att_finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_o, tm_w, tm_out, p);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;

@@ -41,17 +41,31 @@ namespace b200 {
 
 namespace {
 
+// 1: q, k and vT tiles are staged in shared memory and written with TMA stores (one elected
+// thread, two 16 KiB boxes each); 0: every thread stores its row's 64-byte pieces itself, so a
+// warp's store instruction touches 32 cache lines and the L1 pipe bounds the kernel.
+#ifndef B200_APROJ_TMASTORE
+#define B200_APROJ_TMASTORE 1
+#endif
+#if B200_APROJ_TMASTORE
+constexpr int XSTAGES = 2;
+#else
 constexpr int XSTAGES = 3;
+#endif
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
 constexpr int W_BYTES = 8 * SLAB_BYTES;  // rows 0..255 [Wq|Wk], 256..383 Wv, 384..399 Wb, rest zero
 constexpr int LN_WARPS = 8;  // two threads per pair
 constexpr int THREADS = 64 + LN_WARPS * 32 + 128;
+constexpr int EPI_THREAD0 = 64 + LN_WARPS * 32;  // first thread of the epilogue warps
 constexpr uint32_t TM_QK = 0, TM_V = 256, TM_B = 384;
 enum { G_QK = 0, G_B = 1, G_V = 2 };
 
 struct Smem {
   uint8_t w[W_BYTES];
   uint8_t x[XSTAGES][TILE_BYTES];
+#if B200_APROJ_TMASTORE
+  uint8_t out[TILE_BYTES];  // staging of one 32 KiB output tile (q, then k, then vT)
+#endif
   uint32_t gamma2[64];
   uint32_t beta2[64];
   uint64_t w_full, x_full[XSTAGES], xn_full[XSTAGES], x_empty[XSTAGES], acc_full[3], acc_empty[3];
@@ -77,6 +91,8 @@ struct Params {
 
 __global__ void __launch_bounds__(THREADS, 1)
 att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                   const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_vt,
                    const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -221,10 +237,54 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       const int o = static_cast<int>(tile / p.tiles_inner);
       const int t0 = static_cast<int>(tile % p.tiles_inner) * 128;
       const int t = t0 + row;
+#if !B200_APROJ_TMASTORE
       const long long pair_off = (static_cast<long long>(o) * p.n_inner + t) * 128;
+#endif
       // ---- q and k: thread = pair, 128 + 128 channels
+#if B200_APROJ_TMASTORE
+      // (votes: the outcome of each bounded wait is made the same for all 128 threads, which
+      // meet at named barriers around the staging buffer)
+      if (!named_barrier_and(1, 128, mbar_wait(&sm.acc_full[G_QK], it & 1, p.status, ST_TIMEOUT_EPILOGUE))) break;
+#else
       if (!mbar_wait(&sm.acc_full[G_QK], it & 1, p.status, ST_TIMEOUT_EPILOGUE)) break;
+#endif
       tc_fence_after();
+#if B200_APROJ_TMASTORE
+#pragma unroll 1
+      for (int part = 0; part < 2; ++part) {  // q, then k: one staged 32 KiB tile each
+        if (threadIdx.x == EPI_THREAD0) tma_store_wait_read();
+        named_barrier(1, 128);
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + TM_QK + (part * 4 + c4) * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            uint32_t u[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint32_t v2 = pack_bf16x2(__uint_as_float(r[8 * g4 + 2 * e]), __uint_as_float(r[8 * g4 + 2 * e + 1]));
+              // q / sqrt(d) as the product with the rounded reciprocal: the same bf16 as the true
+              // division for every bf16 q (the quotient is never within 1e-5 of a rounding boundary)
+              if (part == 0) v2 = pack_bf16x2(bf16_lo(v2) * q_inv, bf16_hi(v2) * q_inv);
+              u[e] = v2;
+            }
+            // row = pair, 16-byte chunk = 8 channels: channels 32*c4 + 8*g4 .. +7
+            *reinterpret_cast<uint4*>(sm.out + (c4 >> 1) * SLAB_BYTES + sw128_offset(row, (c4 & 1) * 4 + g4)) =
+                make_uint4(u[0], u[1], u[2], u[3]);
+          }
+        }
+        fence_proxy_async();
+        named_barrier(1, 128);
+        if (threadIdx.x == EPI_THREAD0) {  // pairs past n_inner are outside the tensor and are not written
+          const CUtensorMap* tm = part ? &tm_k : &tm_q;
+          tma_store_3d(tm, sm.out, 0, t0, o);
+          tma_store_3d(tm, sm.out + SLAB_BYTES, 64, t0, o);
+          tma_store_commit();
+        }
+      }
+#else
 #pragma unroll 1
       for (int chunk = 0; chunk < 8; ++chunk) {
         uint32_t r[32];
@@ -252,11 +312,16 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           }
         }
       }
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[G_QK]);
       // ---- bias: thread = pair, 4 heads
+#if B200_APROJ_TMASTORE
+      if (!named_barrier_and(1, 128, mbar_wait(&sm.acc_full[G_B], it & 1, p.status, ST_TIMEOUT_EPILOGUE))) break;
+#else
       if (!mbar_wait(&sm.acc_full[G_B], it & 1, p.status, ST_TIMEOUT_EPILOGUE)) break;
+#endif
       tc_fence_after();
       {
         uint32_t r[16];
@@ -273,8 +338,43 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[G_B]);
       // ---- vT: thread = channel, 128 pairs -> one contiguous run of the row
+#if B200_APROJ_TMASTORE
+      if (!named_barrier_and(1, 128, mbar_wait(&sm.acc_full[G_V], it & 1, p.status, ST_TIMEOUT_EPILOGUE))) break;
+#else
       if (!mbar_wait(&sm.acc_full[G_V], it & 1, p.status, ST_TIMEOUT_EPILOGUE)) break;
+#endif
       tc_fence_after();
+#if B200_APROJ_TMASTORE
+      if (threadIdx.x == EPI_THREAD0) tma_store_wait_read();
+      named_barrier(1, 128);
+#pragma unroll 1
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + TM_V + chunk * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          uint32_t u[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = 8 * g4 + 2 * e;
+            const uint32_t b2 = pack_bf16x2(__uint_as_float(r[c]), __uint_as_float(r[c + 1]));  // bf16(xn @ Wv)
+            const __half2 h2 = __floats2half2_rn(bf16_lo(b2), bf16_hi(b2));
+            u[e] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+          // row = channel, 16-byte chunk = 8 pairs: pairs 32*chunk + 8*g4 .. +7 of the tile
+          *reinterpret_cast<uint4*>(sm.out + (chunk >> 1) * SLAB_BYTES + sw128_offset(row, (chunk & 1) * 4 + g4)) =
+              make_uint4(u[0], u[1], u[2], u[3]);
+        }
+      }
+      fence_proxy_async();
+      named_barrier(1, 128);
+      if (threadIdx.x == EPI_THREAD0) {
+        tma_store_3d(&tm_vt, sm.out, t0, 0, o);
+        if (t0 + 64 < p.n_inner) tma_store_3d(&tm_vt, sm.out + SLAB_BYTES, t0 + 64, 0, o);
+        tma_store_commit();
+      }
+#else
       __half* vrow = p.vt + (static_cast<long long>(o) * 128 + row) * p.ld + t0;
 #pragma unroll 1
       for (int chunk = 0; chunk < 4; ++chunk) {
@@ -303,12 +403,16 @@ att_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
         }
       }
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[G_V]);
     }
   }
 
+#if B200_APROJ_TMASTORE
+  if (threadIdx.x == EPI_THREAD0) tma_store_wait_all();
+#endif
   if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);
   tc_fence_before();
@@ -353,7 +457,23 @@ extern "C" int b200tri_triatt_project(const b200tri_triatt_project_args* a, b200
   pack_copy_words(a->norm_scale, gamma2, 64, stream);
   pack_copy_words(a->norm_bias, beta2, 64, stream);
 
-  CUtensorMap tm_x, tm_w;
+  CUtensorMap tm_x, tm_w, tm_q, tm_k, tm_vt;
+  {  // q and k [n_outer][n_inner][128], written as tiles of [128 pairs][64 channels]
+    const uint64_t dims[3] = {128, (uint64_t)a->n_inner, (uint64_t)a->n_outer};
+    const uint64_t str[2] = {256, (uint64_t)a->n_inner * 256};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = make_tmap(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+    rc = make_tmap(&tm_k, a->k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
+  {  // vT [n_outer][128][ld] fp16, written as tiles of [128 channels][64 pairs]
+    const uint64_t dims[3] = {(uint64_t)a->n_inner, 128, (uint64_t)a->n_outer};
+    const uint64_t str[2] = {(uint64_t)a->ld * 2, (uint64_t)a->ld * 2 * 128};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = make_tmap(&tm_vt, a->vt, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
   {
     const uint64_t dims[3] = {128, (uint64_t)a->n_inner, (uint64_t)a->n_outer};
     const uint64_t str[2] = {(uint64_t)a->xs_inner * 2, (uint64_t)a->xs_outer * 2};
@@ -393,7 +513,7 @@ extern "C" int b200tri_triatt_project(const b200tri_triatt_project_args* a, b200
   {
     TimedLaunch timed(K_TRIATT_PROJECT, stream);
     count_launch();
-    att_project_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_w, p);
+    att_project_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_w, tm_q, tm_k, tm_vt, p);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;

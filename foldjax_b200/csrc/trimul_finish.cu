@@ -30,11 +30,21 @@ namespace {
 constexpr int STAGES = 2;
 constexpr int TILE_BYTES = 2 * SLAB_BYTES;
 constexpr int THREADS = 320;
+constexpr int EPI_THREAD0 = 192;  // first thread of the epilogue warps
+// 1: the epilogue stages the output tile in shared memory ([128 pairs][128 channels] as two
+// swizzled slabs) and writes it with two TMA stores; 0: every thread stores its pair's row
+// itself, 64 bytes at a time, so that a warp's store instruction touches 32 cache lines.
+#ifndef B200_FIN_TMASTORE
+#define B200_FIN_TMASTORE 1
+#endif
 
 struct Smem {
   uint8_t w[4 * SLAB_BYTES];  // g_out^T (2 slabs), p_out^T (2 slabs)
   uint8_t x[STAGES][TILE_BYTES];
   uint8_t t[STAGES][TILE_BYTES];
+#if B200_FIN_TMASTORE
+  uint8_t out[TILE_BYTES];
+#endif
   uint32_t gamma_in[64], beta_in[64], gamma_out[64], beta_out[64];
   uint64_t w_full, in_full[STAGES], xn_full[STAGES], in_empty[STAGES], col_read[STAGES], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
@@ -55,7 +65,8 @@ struct FinishParams {
 
 __global__ void __launch_bounds__(THREADS, 1)
 finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_t,
-              const __grid_constant__ CUtensorMap tm_w, const FinishParams p) {
+              const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_out,
+              const FinishParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
@@ -192,7 +203,14 @@ finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const int i = static_cast<int>(tile / p.tiles_j);
       const int j = static_cast<int>(tile % p.tiles_j) * 128 + pr;
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+#if B200_FIN_TMASTORE
+      // the previous tile must have left the staging buffer; the vote makes the outcome of the
+      // bounded wait the same for all 128 threads, which meet at a barrier below
+      if (threadIdx.x == EPI_THREAD0) tma_store_wait_read();
+      if (!named_barrier_and(1, 128, mbar_wait(&sm.acc_full[acc], acc_phase, p.status, ST_TIMEOUT_EPILOGUE))) break;
+#else
       if (!mbar_wait(&sm.acc_full[acc], acc_phase, p.status, ST_TIMEOUT_EPILOGUE)) break;
+#endif
       tc_fence_after();
       const long long off = static_cast<long long>(i) * p.os_i + static_cast<long long>(j) * p.os_j;
 #pragma unroll 1
@@ -202,7 +220,9 @@ finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         tmem_ld32(lane_addr + acc * 256 + 128 + chunk * 32, o);
         tmem_ld_wait();
         if (j < p.n_j) {
+#if !B200_FIN_TMASTORE
           uint4* dst = reinterpret_cast<uint4*>(p.out + off + chunk * 32);
+#endif
           const uint4* res = p.residual ? reinterpret_cast<const uint4*>(p.residual + off + chunk * 32) : nullptr;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -221,16 +241,34 @@ finish_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               u[2] = bf16x2_add(rv.z, u[2]);
               u[3] = bf16x2_add(rv.w, u[3]);
             }
+#if B200_FIN_TMASTORE
+            *reinterpret_cast<uint4*>(sm.out + (chunk >> 1) * SLAB_BYTES + sw128_offset(pr, (chunk & 1) * 4 + q)) =
+                make_uint4(u[0], u[1], u[2], u[3]);
+#else
             dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+#endif
           }
         }
       }
+#if B200_FIN_TMASTORE
+      fence_proxy_async();
+      named_barrier(1, 128);
+      if (threadIdx.x == EPI_THREAD0) {  // rows past n_j are outside the tensor and are not written
+        const int j0 = static_cast<int>(tile % p.tiles_j) * 128;
+        tma_store_3d(&tm_out, sm.out, 0, j0, i);
+        tma_store_3d(&tm_out, sm.out + SLAB_BYTES, 64, j0, i);
+        tma_store_commit();
+      }
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
     }
   }
 
+#if B200_FIN_TMASTORE
+  if (threadIdx.x == EPI_THREAD0) tma_store_wait_all();
+#endif
   if (*reinterpret_cast<volatile int*>(p.status) != ST_OK)
     for (int i = 0; i < 100; ++i) __nanosleep(1000);
   tc_fence_before();
@@ -272,7 +310,14 @@ extern "C" int b200tri_trimul_finish(const b200tri_trimul_finish_args* a, b200tr
   pack_copy_words(a->norm_out_scale, ln + 128, 64, stream);
   pack_copy_words(a->norm_out_bias, ln + 192, 64, stream);
 
-  CUtensorMap tm_x, tm_t, tm_w;
+  CUtensorMap tm_x, tm_t, tm_w, tm_out;
+  {
+    const uint64_t dims[3] = {128, (uint64_t)a->n_j, (uint64_t)a->n_i};
+    const uint64_t str[2] = {(uint64_t)a->os_j * 2, (uint64_t)a->os_i * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = make_tmap(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
   {
     const uint64_t dims[3] = {128, (uint64_t)a->n_j, (uint64_t)a->n_i};
     const uint64_t str[2] = {(uint64_t)a->xs_j * 2, (uint64_t)a->xs_i * 2};
@@ -322,7 +367,7 @@ extern "C" int b200tri_trimul_finish(const b200tri_trimul_finish_args* a, b200tr
   {
     TimedLaunch timed(K_TRIMUL_FINISH, stream);
     count_launch();
-    finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_t, tm_w, p);
+    finish_kernel<<<static_cast<unsigned>(grid), THREADS, sizeof(Smem), stream>>>(tm_x, tm_t, tm_w, tm_out, p);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200TRI_OK;

@@ -87,12 +87,9 @@ class _Prec:
 
 
 def _sigmoid(x: np.ndarray) -> np.ndarray:
-    out = np.empty_like(x)
-    pos = x >= 0
-    out[pos] = 1.0 / (1.0 + np.exp(-x[pos]))
-    e = np.exp(x[~pos])
-    out[~pos] = e / (1.0 + e)
-    return out
+    """Overflow-free logistic: 1 / (1 + exp(-x)) for x >= 0 and exp(x) / (1 + exp(x)) below."""
+    e = np.exp(-np.abs(x))
+    return np.where(x >= 0, 1.0 / (1.0 + e), e / (1.0 + e)).astype(x.dtype, copy=False)
 
 
 def layer_norm(x: np.ndarray, scale: np.ndarray, bias: np.ndarray, eps: float, dtype: str = "float64") -> np.ndarray:
@@ -168,6 +165,7 @@ def attention_core(
     mask_bias: np.ndarray,
     dtype: str = "float64",
     row_chunk: int = 16,
+    threads: int | None = None,
 ) -> np.ndarray:
     """triangle_attention.py:428-455.
 
@@ -185,7 +183,8 @@ def attention_core(
     mb = np.asarray(mask_bias, dtype=work)
     out = np.empty_like(q)
     n_i = q.shape[1]
-    for s in range(0, n_i, row_chunk):
+
+    def rows(s: int) -> None:
         e = min(n_i, s + row_chunk)
         scores = np.matmul(q[:, s:e], np.swapaxes(k[:, s:e], -1, -2))
         scores = scores + mb[:, s:e] + tb  # that order: :453
@@ -193,6 +192,16 @@ def attention_core(
         p = np.exp(scores)
         p /= p.sum(axis=-1, keepdims=True)
         out[:, s:e] = np.matmul(p, v[:, s:e])
+
+    starts = range(0, n_i, row_chunk)
+    if threads and threads > 1 and len(starts) > 1:  # rows are independent; NumPy releases the GIL in these ops
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=threads) as pool:
+            list(pool.map(rows, starts))
+    else:
+        for s in starts:
+            rows(s)
     return pr.r(out)
 
 
@@ -205,6 +214,7 @@ def triangle_attention(
     eps: float = 1e-5,
     dtype: str = "float64",
     return_parts: bool = False,
+    threads: int | None = None,
 ):
     """triangle_attention.py:79-162 and 346-425 (XLA path).
 
@@ -241,7 +251,7 @@ def triangle_attention(
     q, k, v = heads_first(q), heads_first(k), heads_first(v)
     q_scale = pr.r(np.sqrt(np.asarray(c_hidden, dtype=work)))  # sqrt evaluated in the trunk dtype  :399
     q = pr.r(q / q_scale)  # :400
-    o = attention_core(q, k, v, tri_bias, mask_bias, dtype)  # :414
+    o = attention_core(q, k, v, tri_bias, mask_bias, dtype, threads=threads)  # :414
     o = np.swapaxes(o, -2, -3)  # [B,I,J,H,D]
     g = pr.r(_sigmoid(gate)).reshape(gate.shape[:-1] + (heads, c_hidden))  # :421-422
     o = pr.r(o * g)
