@@ -274,7 +274,11 @@ def run_gpu(args) -> None:
             for blk in trunk:
                 zz = cp.triangle_block_cp(ctx, blk, zz, mm)
             return zz
-        grid_name = f"2-D context parallel {ctx.grid.rows}x{ctx.grid.cols}, NCCL point-to-point tile exchange"
+        run_block(z, mask)  # sizes the exchange workspace (and maps the peers') before anything is timed
+        pulls = bool(lib.b200tri_comm_pulls(ctx.comm))
+        grid_name = (f"2-D context parallel {ctx.grid.rows}x{ctx.grid.cols}, tiles " +
+                     ("pulled from the peers' mapped workspaces by copy engines (NCCL carries tokens only)" if pulls
+                      else "exchanged with NCCL point-to-point send/receive"))
     z_host = torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True)
     z_host.copy_(z)
     out_host = torch.empty_like(z_host).pin_memory()

@@ -289,6 +289,8 @@ SIGNATURES = {
     "b200tri_comm_destroy": (C.c_int, [C.c_void_p]),
     "b200tri_comm_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                     C.POINTER(C.c_int32)]),
+    "b200tri_comm_workspace": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "b200tri_comm_pulls": (C.c_int, [C.c_void_p]),
     "b200tri_comm_group_start": (C.c_int, []),
     "b200tri_comm_group_end": (C.c_int, []),
     "b200tri_comm_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

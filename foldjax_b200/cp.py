@@ -21,6 +21,7 @@ row-sharded layout of the reference (triangle_attention.py:165-280) up to a tran
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Any, Callable, Mapping
 
@@ -167,6 +168,29 @@ def _ws(tag: str, nbytes: int) -> tuple[int, int]:
     return dev.aligned_ptr(raw), nbytes
 
 
+#: How tiles travel between GPUs. "pull" (default): the communicator owns the exchange workspace,
+#: the peers' workspaces are mapped through CUDA IPC and every rank copies the tiles it needs out
+#: of their owners' memory (copy engines; NCCL only carries ready / consumed tokens). "nccl": tiles
+#: are sent and received by NCCL into a workspace this module allocates.
+TRANSPORT = os.environ.get("B200TRI_CP_TRANSPORT", "nccl").lower()
+
+
+def _exchange_workspace(ctx: CPContext, n: int) -> tuple[int | None, int]:
+    """(workspace pointer or None, bytes) for the two context-parallel ops at ``n`` tokens. None
+    selects the communicator's own workspace, sized here for both ops (collective: every rank
+    reaches this call with the same ``n`` at the same point of its op sequence)."""
+    lib = _lib.load()
+    need = max(lib.b200tri_trimul_cp_workspace_bytes(C.c_void_p(ctx.comm), n),
+               lib.b200tri_triatt_cp_workspace_bytes(C.c_void_p(ctx.comm), n))
+    if TRANSPORT == "nccl":
+        return _ws("cp_exchange", need)
+    if TRANSPORT != "pull":
+        raise ValueError(f"B200TRI_CP_TRANSPORT must be 'pull' or 'nccl', got {TRANSPORT!r}")
+    out = C.c_void_p()
+    _lib.check(lib.b200tri_comm_workspace(C.c_void_p(ctx.comm), need, C.byref(out)))
+    return None, 0
+
+
 def _tile_checks(ctx: CPContext, x: torch.Tensor, mask, residual, out) -> tuple[int, torch.Tensor]:
     if ctx.comm is None:
         raise RuntimeError("this context has no communicator (created without a CUDA device)")
@@ -211,7 +235,7 @@ def triangle_multiplication_cp(
     lv = {k: _leaf(params, *k.split(".")) for k in (
         "norm_in.scale", "norm_in.bias", "p_in.kernel", "g_in.kernel", "norm_out.scale", "norm_out.bias",
         "p_out.kernel", "g_out.kernel")}
-    wp, wb = _ws("cp_trimul", lib.b200tri_trimul_cp_workspace_bytes(C.c_void_p(ctx.comm), n))
+    wp, wb = _exchange_workspace(ctx, n)
     args = _lib.TrimulCpArgs(
         n=n, incoming=int(direction == "incoming"), eps=float(eps), x=x.data_ptr(),
         mask=None if mask is None else mask.data_ptr(),
@@ -250,7 +274,7 @@ def triangle_attention_cp(
     lv = {k: _leaf(params, *k.split(".")) for k in (
         "layer_norm.scale", "layer_norm.bias", "linear.kernel", "mha.linear_q.kernel", "mha.linear_k.kernel",
         "mha.linear_v.kernel", "mha.linear_g.kernel", "mha.linear_o.kernel")}
-    wp, wb = _ws("cp_triatt", lib.b200tri_triatt_cp_workspace_bytes(C.c_void_p(ctx.comm), n))
+    wp, wb = _exchange_workspace(ctx, n)
     args = _lib.TriattCpArgs(
         n=n, starting=int(bool(starting)), heads=4, head_dim=32, inf=float(inf), eps=float(eps), x=x.data_ptr(),
         mask=None if mask is None else mask.data_ptr(),

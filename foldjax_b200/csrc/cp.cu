@@ -30,6 +30,15 @@ struct b200tri_comm {
   int world = 0, rank = 0, rows = 0, cols = 0, m = 0, r = 0, c = 0, device = 0;
   cudaStream_t stream = nullptr;  // exchange stream
   cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr;
+  // Exchange workspace owned by the communicator (b200tri_comm_workspace) and, one process
+  // per GPU, the peers' workspaces mapped into this process through CUDA IPC: tiles are then
+  // pulled with device-to-device copies on the copy engines instead of NCCL's send/receive
+  // kernels, and NCCL only carries the "tile ready" / "tile consumed" tokens.
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  std::vector<void*> peer_ws;  // [world], nullptr where not mapped (own rank, or no IPC)
+  uint8_t* tokens = nullptr;   // device: 64-byte send slot + world x 64-byte receive slots
+  bool one_process = false;    // created by b200tri_comm_init_all
 };
 
 namespace b200 {
@@ -146,7 +155,7 @@ std::vector<Msg> build_plan(const Grid& g, int op) {
 }
 
 struct Piece {
-  void* ptr;
+  size_t off;  // byte offset inside the workspace (of the rank whose array it is)
   size_t bytes;
 };
 
@@ -162,38 +171,83 @@ struct Offsets {
   size_t total() const { return (off + 1023) / 1024 * 1024; }
 };
 
-// Post this rank's share of `msgs` (those accepted by `want`): receives and sends as one NCCL
-// group on the exchange stream, local messages as device copies on the caller's stream.
+// Post this rank's share of `msgs` (those accepted by `want`). `views(msg, send, who, out)`
+// lists the pieces of a message as offsets into the workspace: on the send side inside the
+// workspace of rank `who` = msg.src, on the receive side inside this rank's. Local messages
+// are device copies on the caller's stream. Remote ones travel
+//  * as one NCCL group of sends and receives on the exchange stream, or
+//  * when every peer's workspace is mapped here (`pull`): the receiver copies each piece out
+//    of the sender's workspace with a device-to-device copy (copy engines, full NVLink rate);
+//    NCCL carries a 4-byte "ready" token from sender to receiver before the copies and a
+//    "consumed" token back after them, so a sender never overwrites a tile that is being read.
 template <typename Want, typename Views>
-int post_exchange(b200tri_comm* cm, const std::vector<Msg>& msgs, Want want, Views views, cudaStream_t compute) {
+int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Msg>& msgs, Want want, Views views,
+                  cudaStream_t compute) {
   const Nccl* api = nccl_api();
   B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
   std::vector<Piece> send, recv;
-  bool grouped = false;
-  // with timing on, the span of this group on the exchange stream (it starts when the stream
+  // with timing on, the span of this exchange on the exchange stream (it starts when the stream
   // has seen the caller's "tiles are ready" event, so it is transfer time plus peer skew)
   TimedLaunch timed(K_CP_EXCHANGE, cm->stream);
+  auto remote = [&](const Msg& msg) {
+    return want(msg) && msg.src != msg.dst && (msg.src == cm->rank || msg.dst == cm->rank);
+  };
+  // local messages
   for (const Msg& msg : msgs) {
-    if (!want(msg) || (msg.src != cm->rank && msg.dst != cm->rank)) continue;
+    if (!want(msg) || msg.src != cm->rank || msg.dst != cm->rank) continue;
     send.clear();
     recv.clear();
-    if (msg.src == cm->rank) views(msg, true, send);
-    if (msg.dst == cm->rank) views(msg, false, recv);
-    if (msg.src == cm->rank && msg.dst == cm->rank) {
-      for (size_t i = 0; i < send.size(); ++i)
-        if (send[i].ptr != recv[i].ptr)
-          B200_CUDA_OK(cudaMemcpyAsync(recv[i].ptr, send[i].ptr, send[i].bytes, cudaMemcpyDeviceToDevice, compute));
-      continue;
-    }
-    if (!grouped) {
-      B200_NCCL_OK(api, api->GroupStart());
-      grouped = true;
-    }
-    for (const Piece& p : send) B200_NCCL_OK(api, api->Send(p.ptr, p.bytes, ncclUint8, msg.dst, cm->nccl, cm->stream));
-    for (const Piece& p : recv) B200_NCCL_OK(api, api->Recv(p.ptr, p.bytes, ncclUint8, msg.src, cm->nccl, cm->stream));
+    views(msg, true, cm->rank, send);
+    views(msg, false, cm->rank, recv);
+    for (size_t i = 0; i < send.size(); ++i)
+      if (send[i].off != recv[i].off)
+        B200_CUDA_OK(cudaMemcpyAsync(ws + recv[i].off, ws + send[i].off, send[i].bytes, cudaMemcpyDeviceToDevice, compute));
   }
-  if (grouped) B200_NCCL_OK(api, api->GroupEnd());
-  return B200TRI_OK;
+  bool any = false;
+  for (const Msg& msg : msgs) any = any || remote(msg);
+  if (!any) return B200TRI_OK;
+  if (!pull) {
+    B200_NCCL_OK(api, api->GroupStart());
+    for (const Msg& msg : msgs) {
+      if (!remote(msg)) continue;
+      send.clear();
+      recv.clear();
+      if (msg.src == cm->rank) views(msg, true, cm->rank, send);
+      if (msg.dst == cm->rank) views(msg, false, cm->rank, recv);
+      for (const Piece& p : send) B200_NCCL_OK(api, api->Send(ws + p.off, p.bytes, ncclUint8, msg.dst, cm->nccl, cm->stream));
+      for (const Piece& p : recv) B200_NCCL_OK(api, api->Recv(ws + p.off, p.bytes, ncclUint8, msg.src, cm->nccl, cm->stream));
+    }
+    B200_NCCL_OK(api, api->GroupEnd());
+    return B200TRI_OK;
+  }
+  // tokens: slot 0 is what this rank sends, slot 1 + peer what it receives from that peer
+  auto token_round = [&](bool ready) -> int {
+    B200_NCCL_OK(api, api->GroupStart());
+    for (const Msg& msg : msgs) {
+      if (!remote(msg)) continue;
+      const bool i_send = ready ? msg.src == cm->rank : msg.dst == cm->rank;
+      const int peer = msg.src == cm->rank ? msg.dst : msg.src;
+      if (i_send)
+        B200_NCCL_OK(api, api->Send(cm->tokens, 4, ncclUint8, peer, cm->nccl, cm->stream));
+      else
+        B200_NCCL_OK(api, api->Recv(cm->tokens + 64 * (1 + peer), 4, ncclUint8, peer, cm->nccl, cm->stream));
+    }
+    B200_NCCL_OK(api, api->GroupEnd());
+    return B200TRI_OK;
+  };
+  int rc = token_round(true);  // every sender's tiles are complete
+  if (rc) return rc;
+  for (const Msg& msg : msgs) {
+    if (!remote(msg) || msg.dst != cm->rank) continue;
+    send.clear();
+    recv.clear();
+    views(msg, true, msg.src, send);
+    views(msg, false, cm->rank, recv);
+    const uint8_t* from = static_cast<const uint8_t*>(cm->peer_ws[msg.src]);
+    for (size_t i = 0; i < send.size(); ++i)
+      B200_CUDA_OK(cudaMemcpyAsync(ws + recv[i].off, from + send[i].off, send[i].bytes, cudaMemcpyDeviceToDevice, cm->stream));
+  }
+  return token_round(false);  // every tile has been read: the senders may reuse their buffers
 }
 
 int check_comm(const b200tri_comm* cm, const char* who) {
@@ -218,7 +272,33 @@ int finish_init(b200tri_comm* cm, int world, int rank, int rows, int cols) {
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_ready, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_first, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_rest, cudaEventDisableTiming));
+  B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&cm->tokens), 64 * (1 + static_cast<size_t>(world))));
+  B200_CUDA_OK(cudaMemset(cm->tokens, 0, 64 * (1 + static_cast<size_t>(world))));
   return B200TRI_OK;
+}
+
+// Every rank contributes 64 bytes (`mine`) and receives every rank's into all[world][64]:
+// an all-gather over the communicator's send/receive path. Host-synchronous (set-up only).
+int gather_64(b200tri_comm* cm, const void* mine, uint8_t* all) {
+  const Nccl* api = nccl_api();
+  B200_CUDA_OK(cudaMemcpyAsync(cm->tokens, mine, 64, cudaMemcpyHostToDevice, cm->stream));
+  B200_NCCL_OK(api, api->GroupStart());
+  for (int peer = 0; peer < cm->world; ++peer) {
+    if (peer == cm->rank) continue;
+    B200_NCCL_OK(api, api->Send(cm->tokens, 64, ncclUint8, peer, cm->nccl, cm->stream));
+    B200_NCCL_OK(api, api->Recv(cm->tokens + 64 * (1 + peer), 64, ncclUint8, peer, cm->nccl, cm->stream));
+  }
+  B200_NCCL_OK(api, api->GroupEnd());
+  B200_CUDA_OK(cudaMemcpyAsync(all, cm->tokens + 64, 64 * static_cast<size_t>(cm->world), cudaMemcpyDeviceToHost, cm->stream));
+  B200_CUDA_OK(cudaStreamSynchronize(cm->stream));
+  memcpy(all + 64 * static_cast<size_t>(cm->rank), mine, 64);
+  return B200TRI_OK;
+}
+
+void unmap_peers(b200tri_comm* cm) {
+  for (void* p : cm->peer_ws)
+    if (p) cudaIpcCloseMemHandle(p);
+  cm->peer_ws.clear();
 }
 
 int check_grid(int world, int rows, int cols) {
@@ -386,6 +466,7 @@ extern "C" int b200tri_comm_init_all(b200tri_comm** out, const int32_t* devices,
   for (int i = 0; i < world; ++i) {
     out[i] = new b200tri_comm;
     out[i]->nccl = comms[i];
+    out[i]->one_process = true;
     B200_CUDA_OK(cudaSetDevice(devs[i]));
     rc = finish_init(out[i], world, i, rows, cols);
     if (rc) break;
@@ -401,6 +482,9 @@ extern "C" int b200tri_comm_destroy(b200tri_comm* cm) {
   cudaGetDevice(&prev);
   cudaSetDevice(cm->device);
   if (cm->stream) cudaStreamSynchronize(cm->stream);
+  unmap_peers(cm);
+  if (cm->ws) cudaFree(cm->ws);
+  if (cm->tokens) cudaFree(cm->tokens);
   if (cm->nccl && api) api->CommDestroy(cm->nccl);
   if (cm->ev_ready) cudaEventDestroy(cm->ev_ready);
   if (cm->ev_first) cudaEventDestroy(cm->ev_first);
@@ -410,6 +494,55 @@ extern "C" int b200tri_comm_destroy(b200tri_comm* cm) {
   delete cm;
   return B200TRI_OK;
 }
+
+// The communicator's own exchange workspace: (re)allocated here - set-up time, never inside an
+// op - and, with one process per GPU, mapped into every peer through CUDA IPC, so that the ops
+// can pull tiles with device-to-device copies. Collective: every rank calls it with the same
+// size at the same point. Host-synchronous.
+extern "C" int b200tri_comm_workspace(b200tri_comm* cm, size_t bytes, void** out) {
+  int rc = check_comm(cm, "comm_workspace");
+  if (rc) return rc;
+  B200_REQUIRE(out != nullptr && bytes > 0, B200TRI_ERR_INVALID, "comm_workspace: null result pointer or zero size");
+  if (cm->ws && cm->ws_bytes >= bytes) {
+    *out = cm->ws;
+    return B200TRI_OK;
+  }
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  unmap_peers(cm);
+  if (cm->ws) B200_CUDA_OK(cudaFree(cm->ws));
+  cm->ws = nullptr;
+  cm->ws_bytes = 0;
+  B200_CUDA_OK(cudaMalloc(&cm->ws, bytes));
+  cm->ws_bytes = bytes;
+  *out = cm->ws;
+  if (cm->one_process || cm->world == 1) return B200TRI_OK;  // tiles travel as NCCL sends / receives
+  // exchange the IPC handles, map the peers, and agree on the outcome
+  cudaIpcMemHandle_t mine;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  B200_CUDA_OK(cudaIpcGetMemHandle(&mine, cm->ws));
+  std::vector<uint8_t> all(64 * static_cast<size_t>(cm->world));
+  if ((rc = gather_64(cm, &mine, all.data()))) return rc;
+  cm->peer_ws.assign(cm->world, nullptr);
+  uint8_t ok[64] = {1};
+  for (int peer = 0; peer < cm->world; ++peer) {
+    if (peer == cm->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, all.data() + 64 * static_cast<size_t>(peer), 64);
+    if (cudaIpcOpenMemHandle(&cm->peer_ws[peer], h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      cm->peer_ws[peer] = nullptr;
+      ok[0] = 0;
+    }
+  }
+  if ((rc = gather_64(cm, ok, all.data()))) return rc;
+  for (int peer = 0; peer < cm->world; ++peer)
+    if (all[64 * static_cast<size_t>(peer)] == 0) ok[0] = 0;
+  if (!ok[0]) unmap_peers(cm);  // some rank could not map a peer: every rank stays on sends / receives
+  return B200TRI_OK;
+}
+
+// 1 if the ops called with workspace = NULL pull their tiles through mapped peer memory.
+extern "C" int b200tri_comm_pulls(const b200tri_comm* cm) { return cm && !cm->peer_ws.empty() ? 1 : 0; }
 
 extern "C" int b200tri_comm_info(const b200tri_comm* cm, int32_t* world, int32_t* rank, int32_t* rows, int32_t* cols) {
   B200_REQUIRE(cm != nullptr, B200TRI_ERR_INVALID, "comm_info: null communicator");
@@ -448,13 +581,14 @@ extern "C" int b200tri_comm_probe(b200tri_comm* cm, const void* shard, void* gat
     for (int src = 0; src < cm->world; ++src) msgs.push_back({src, dst, WHAT_A, -1, src, 0});
   B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
   B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  // absolute addresses as "offsets" from a null base; always the NCCL path (the probe tests it)
   rc = post_exchange(
-      cm, msgs, [](const Msg&) { return true; },
-      [&](const Msg& msg, bool send, std::vector<Piece>& out) {
+      cm, nullptr, false, msgs, [](const Msg&) { return true; },
+      [&](const Msg& msg, bool send, int, std::vector<Piece>& out) {
         if (send)
-          out.push_back({const_cast<void*>(shard), bytes});
+          out.push_back({reinterpret_cast<size_t>(shard), bytes});
         else
-          out.push_back({static_cast<uint8_t*>(gathered) + static_cast<size_t>(msg.slot0) * bytes, bytes});
+          out.push_back({reinterpret_cast<size_t>(gathered) + static_cast<size_t>(msg.slot0) * bytes, bytes});
       },
       stream);
   if (rc) return rc;
@@ -480,12 +614,17 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   if ((rc = tile_dims(cm, a->n, &d))) return rc;
   const bool incoming = a->incoming != 0;
   const TrimulPlan pl = trimul_plan(cm, d, incoming);
-  B200_REQUIRE(a->workspace && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,
-               "trimul_cp: workspace of %zu bytes needed, got %zu", pl.total, a->workspace_bytes);
-  B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
+  // workspace = NULL: the communicator's own exchange workspace (b200tri_comm_workspace), whose
+  // peers' copies are mapped here, so tiles are pulled instead of sent
+  void* ws_ptr = a->workspace ? a->workspace : cm->ws;
+  const size_t ws_have = a->workspace ? a->workspace_bytes : cm->ws_bytes;
+  const bool pull = !a->workspace && !cm->peer_ws.empty();
+  B200_REQUIRE(ws_ptr && ws_have >= pl.total, B200TRI_ERR_WORKSPACE,
+               "trimul_cp: workspace of %zu bytes needed, got %zu", pl.total, ws_have);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(ws_ptr) & 1023) == 0, B200TRI_ERR_INVALID,
                "trimul_cp: workspace must be 1024-byte aligned");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  uint8_t* ws = static_cast<uint8_t*>(ws_ptr);
   const int R = cm->rows, C = cm->cols, m = cm->m, r = cm->r, c = cm->c;
   const int64_t n = d.n, n_r = d.n_r, n_c = d.n_c;
   (void)R;
@@ -525,10 +664,13 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   const std::vector<Msg> msgs =
       build_plan(Grid{cm->rows, cm->cols, m}, incoming ? B200TRI_CP_TRIMUL_INCOMING : B200TRI_CP_TRIMUL_OUTGOING);
   rc = post_exchange(
-      cm, msgs, [](const Msg&) { return true; },
-      [&](const Msg& msg, bool send, std::vector<Piece>& out) {
-        if (send) {
-          uint8_t* src = ws + (msg.what == WHAT_A ? pl.a_loc : pl.b_loc);
+      cm, ws, pull, msgs, [](const Msg&) { return true; },
+      [&](const Msg& msg, bool send, int who, std::vector<Piece>& out) {
+        if (send) {  // the local arrays of rank `who`: the same layout, its own slot positions
+          const int wr = who / cm->cols, wc = who % cm->cols;
+          const size_t a_loc = incoming ? pl.a_loc : pl.a_all + blk_bytes * m * wc;
+          const size_t b_loc = incoming ? pl.b_all + blk_bytes * wr : pl.b_loc;
+          const size_t src = msg.what == WHAT_A ? a_loc : b_loc;
           if (msg.block < 0) {  // a whole local array: m blocks (outgoing a), or one block
             const size_t whole = (!incoming && msg.what == WHAT_A) ? blk_bytes * m : blk_bytes;
             out.push_back({src, whole});
@@ -539,14 +681,14 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
         }
         if (!incoming) {
           if (msg.what == WHAT_A)
-            out.push_back({ws + pl.a_all + blk_bytes * m * msg.slot0, blk_bytes * m});
+            out.push_back({pl.a_all + blk_bytes * m * msg.slot0, blk_bytes * m});
           else
-            out.push_back({ws + pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+            out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
         } else {
           if (msg.what == WHAT_A)
-            out.push_back({ws + pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1), blk_bytes});
+            out.push_back({pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1), blk_bytes});
           else
-            out.push_back({ws + pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+            out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
         }
       },
       stream);
@@ -630,12 +772,15 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   const bool starting = a->starting != 0;
   const TriattPlan pl = triatt_plan(cm, d, starting);
   B200_REQUIRE(pl.tiles <= 1 + 7, B200TRI_ERR_UNSUPPORTED, "triatt_cp: at most 8 key tiles per ring (got %d)", pl.tiles);
-  B200_REQUIRE(a->workspace && a->workspace_bytes >= pl.total, B200TRI_ERR_WORKSPACE,
-               "triatt_cp: workspace of %zu bytes needed, got %zu", pl.total, a->workspace_bytes);
-  B200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 1023) == 0, B200TRI_ERR_INVALID,
+  void* ws_ptr = a->workspace ? a->workspace : cm->ws;
+  const size_t ws_have = a->workspace ? a->workspace_bytes : cm->ws_bytes;
+  const bool pull = !a->workspace && !cm->peer_ws.empty();
+  B200_REQUIRE(ws_ptr && ws_have >= pl.total, B200TRI_ERR_WORKSPACE,
+               "triatt_cp: workspace of %zu bytes needed, got %zu", pl.total, ws_have);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(ws_ptr) & 1023) == 0, B200TRI_ERR_INVALID,
                "triatt_cp: workspace must be 1024-byte aligned");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  uint8_t* ws = static_cast<uint8_t*>(ws_ptr);
   const int m = cm->m, r = cm->r, c = cm->c;
   const int64_t n = d.n, n_r = d.n_r, n_c = d.n_c;
   const int64_t xs_o = starting ? n_c * 128 : 128, xs_i = starting ? 128 : n_c * 128;
@@ -675,30 +820,30 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   const size_t head_rows = static_cast<size_t>(pl.n_outer) * pl.ld * 2;  // one head of the sender's bias
   const size_t qhead = static_cast<size_t>(pl.n_q) * pl.ld * 2;          // one head of a received bias tile
   const size_t chunk = static_cast<size_t>(n_c) * pl.ld * 2;             // n_c bias rows
-  auto views = [&](const Msg& msg, bool send, std::vector<Piece>& out) {
-    if (msg.what == WHAT_KV) {
-      const int slot = send ? pl.own : msg.slot0;
-      out.push_back({ws + pl.k_all + pl.k_tile * slot, pl.k_tile});
-      out.push_back({ws + pl.vt_all + pl.vt_tile * slot, pl.vt_tile});
+  auto views = [&](const Msg& msg, bool send, int who, std::vector<Piece>& out) {
+    if (msg.what == WHAT_KV) {  // the sender's own key tile sits in its own slot
+      const int slot = send ? (starting ? who % cm->cols : who / cm->cols) : msg.slot0;
+      out.push_back({pl.k_all + pl.k_tile * slot, pl.k_tile});
+      out.push_back({pl.vt_all + pl.vt_tile * slot, pl.vt_tile});
       return;
     }
     for (int h = 0; h < 4; ++h) {
       if (starting) {  // row block of the sender's bias -> the whole bias of one key tile
         if (send)
-          out.push_back({ws + pl.bias_loc + head_rows * h + chunk * msg.block, chunk});
+          out.push_back({pl.bias_loc + head_rows * h + chunk * msg.block, chunk});
         else
-          out.push_back({ws + pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h, chunk});
+          out.push_back({pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h, chunk});
       } else {  // the sender's whole bias -> one query block of one key tile
         if (send)
-          out.push_back({ws + pl.bias_loc + head_rows * h, chunk});
+          out.push_back({pl.bias_loc + head_rows * h, chunk});
         else
-          out.push_back({ws + pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h + chunk * msg.slot1, chunk});
+          out.push_back({pl.bias_all + pl.bias_tile * msg.slot0 + qhead * h + chunk * msg.slot1, chunk});
       }
     }
   };
-  if ((rc = post_exchange(cm, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
+  if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
   B200_CUDA_OK(cudaEventRecord(cm->ev_first, cm->stream));
-  if ((rc = post_exchange(cm, msgs, [](const Msg& x) { return x.what == WHAT_KV; }, views, stream))) return rc;
+  if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_KV; }, views, stream))) return rc;
   B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
 
   // key tiles: the own one first, then the peers' in rotated order (every sender serves a

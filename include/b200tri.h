@@ -425,6 +425,19 @@ int b200tri_comm_info(const b200tri_comm* comm, int32_t* world, int32_t* rank, i
 int b200tri_comm_group_start(void);
 int b200tri_comm_group_end(void);
 
+/* Optional: an exchange workspace owned by the communicator. Collective and host-synchronous
+ * (set-up time: it allocates), every rank with the same size; *ptr is the rank's workspace.
+ * With one process per GPU the peers' workspaces are mapped into this process through CUDA
+ * IPC, and b200tri_trimul_cp / b200tri_triatt_cp called with workspace = NULL then PULL their
+ * tiles out of the owners' workspaces with device-to-device copies (copy engines at NVLink
+ * rate; NCCL only carries 4-byte "ready" / "consumed" tokens) instead of receiving them from
+ * NCCL's send/receive kernels. b200tri_comm_pulls() tells whether that path is active (it is
+ * not when a peer could not be mapped, or under b200tri_comm_init_all: one process sees every
+ * device and keeps to sends and receives). A caller-provided workspace always means sends and
+ * receives. Sizes: the larger of the two *_cp_workspace_bytes. */
+int b200tri_comm_workspace(b200tri_comm* comm, size_t bytes, void** ptr);
+int b200tri_comm_pulls(const b200tri_comm* comm);
+
 /* Mesh self-test, the counterpart of verify_mesh_exchange (src/foldjax/models/_cp.py:199-232):
  * every rank sends `bytes` from `shard` to every other rank and receives theirs into
  * gathered[src * bytes ...] through the very send/receive path the ops use. The caller stamps
@@ -461,7 +474,7 @@ typedef struct {
   const void* g_out;
   const void* residual;
   void* out;
-  void* workspace; /* b200tri_trimul_cp_workspace_bytes(comm, n), 1 KiB aligned */
+  void* workspace; /* b200tri_trimul_cp_workspace_bytes(comm, n), 1 KiB aligned; NULL = the communicator's own */
   size_t workspace_bytes;
 } b200tri_trimul_cp_args;
 
@@ -490,7 +503,7 @@ typedef struct {
   const void* w_o;
   const void* residual;
   void* out;
-  void* workspace; /* b200tri_triatt_cp_workspace_bytes(comm, n), 1 KiB aligned */
+  void* workspace; /* b200tri_triatt_cp_workspace_bytes(comm, n), 1 KiB aligned; NULL = the communicator's own */
   size_t workspace_bytes;
 } b200tri_triatt_cp_args;
 

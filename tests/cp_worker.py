@@ -112,9 +112,11 @@ def main() -> int:
         print("FAILED: repeated call differs", flush=True)
     flag = torch.tensor([failures], device="cuda")
     dist.all_reduce(flag)
+    pulls = bool(_lib.load().b200tri_comm_pulls(ctx.comm))
     ctx.close()
     dist.destroy_process_group()
     if ctx.rank == 0:
+        print(f"transport: {'pull' if pulls else 'nccl'}", flush=True)
         print("CP_WORKER_OK" if flag.item() == 0 else "CP_WORKER_FAILED", flush=True)
     return int(flag.item() != 0)
 

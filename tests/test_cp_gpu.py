@@ -16,10 +16,10 @@ torch = pytest.importorskip("torch")
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def _run(world: int, tokens: int) -> str:
+def _run(world: int, tokens: int, transport: str = "pull") -> str:
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0", B200TRI_CP_TRANSPORT=transport)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(ROOT / "tests" / "cp_worker.py")]
     done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900)
@@ -30,4 +30,15 @@ def _run(world: int, tokens: int) -> str:
 @pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (2, 256), (4, 512), (4, 256), (8, 1024), (8, 256),
                                           (8, 3072)])
 def test_context_parallel_matches_single_gpu(world, tokens):
-    print(_run(world, tokens))
+    """Tiles pulled out of the peers' mapped workspaces (the default transport)."""
+    out = _run(world, tokens)
+    assert "transport: pull" in out, out[-2000:]
+    print(out)
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 256), (4, 512), (8, 1024)])
+def test_context_parallel_over_nccl_send_recv(world, tokens):
+    """The same ops with the tiles sent and received by NCCL into a caller-provided workspace."""
+    out = _run(world, tokens, transport="nccl")
+    assert "transport: nccl" in out, out[-2000:]
+    print(out)
