@@ -230,7 +230,15 @@ def run_gpu(args) -> None:
              for _ in range(args.blocks)]
     params = trunk[0]
     n_pad = args.pad_tokens if args.pad_tokens >= 0 else (n - int(round(n * 3012 / 3072)) if n >= 64 else 0)
-    mask_host = torch.from_numpy(pad_mask(n, n_pad)).pin_memory()
+    pair_mask = pad_mask(n, n_pad)
+    if args.chains:
+        # block-diagonal intra-chain mask: a pair survives only inside one chain (whole key tiles masked)
+        sizes = [int(v) for v in args.chains.split(",")]
+        if sum(sizes) != n:
+            raise SystemExit(f"--chains sizes sum to {sum(sizes)}, not to --tokens {n}")
+        chain = np.repeat(np.arange(len(sizes)), sizes)
+        pair_mask = pair_mask * (chain[:, None] == chain[None, :]).astype(np.float32)[None]
+    mask_host = torch.from_numpy(pair_mask).pin_memory()
     mask = mask_host.cuda()
     s_dev = s_host = tok_mask = None
     if args.full_block:
@@ -396,7 +404,7 @@ def run_gpu(args) -> None:
                          if args.full_block else
                          f"pairformer-triangle-block N={n} c_z=128 4x32 heads (cfg 4 per block): "
                          "tri-mult out+in, tri-attn start+end, residual adds fused"),
-            "tokens": n, "pad_tokens": n_pad, "flops_per_step": flops, "blocks_per_step": args.blocks,
+            "tokens": n, "pad_tokens": n_pad, "chains": args.chains or None, "flops_per_step": flops, "blocks_per_step": args.blocks,
             "pair_transition_in_step": bool(with_transition), "single_track_in_step": bool(args.full_block),
             "parallelism": grid_name,
             "l2": "inputs larger than L2 (pair tensor %.2f GB)" % (n * n * 128 * 2 / 1e9),
@@ -455,6 +463,9 @@ def main() -> None:
                     help="include the pair transition in every block of the step (and in its flop count)")
     ap.add_argument("--pad-tokens", type=int, default=-1,
                     help="trailing padded tokens in the mask (default: the 3012-of-3072 ratio of the headline config)")
+    ap.add_argument("--chains", default="",
+                    help="comma-separated chain lengths: adds a block-diagonal intra-chain pair mask "
+                         "(the second reading of the N=8192 three-chain case)")
     ap.add_argument("--cpu-tokens", type=int, default=384, help="size of the bounded CPU sample")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -172,7 +172,7 @@ def _ws(tag: str, nbytes: int) -> tuple[int, int]:
 #: the peers' workspaces are mapped through CUDA IPC and every rank copies the tiles it needs out
 #: of their owners' memory (copy engines; NCCL only carries ready / consumed tokens). "nccl": tiles
 #: are sent and received by NCCL into a workspace this module allocates.
-TRANSPORT = os.environ.get("B200TRI_CP_TRANSPORT", "nccl").lower()
+TRANSPORT = os.environ.get("B200TRI_CP_TRANSPORT", "pull").lower()
 
 
 def _exchange_workspace(ctx: CPContext, n: int) -> tuple[int | None, int]:
