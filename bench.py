@@ -285,7 +285,8 @@ def run_gpu(args) -> None:
         run_block(z, mask)  # sizes the exchange workspace (and maps the peers') before anything is timed
         pulls = bool(lib.b200tri_comm_pulls(ctx.comm))
         grid_name = (f"2-D context parallel {ctx.grid.rows}x{ctx.grid.cols}, tiles " +
-                     ("pulled from the peers' mapped workspaces by copy engines (NCCL carries tokens only)" if pulls
+                     (f"{cp.TRANSPORT}ed through the peers' mapped workspaces by copy engines, {cp.COPY_STREAMS} copy stream(s) "
+                      "(NCCL carries tokens only)" if pulls
                       else "exchanged with NCCL point-to-point send/receive"))
     z_host = torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True)
     z_host.copy_(z)
@@ -339,6 +340,12 @@ def run_gpu(args) -> None:
     launches = int(lib.b200tri_launch_count() - launches0)
     lib.b200tri_timing_enable(0)
     ktimes = _lib.kernel_times()
+    if world > 1 and rank == 0 and os.environ.get("B200TRI_BENCH_EXCHANGE_TRACE"):
+        # per exchange group of the last step, in order: (whole span, wait for the peers, copies) in ms
+        spans = [_lib.kernel_time_list(k) for k in ("cp_exchange", "cp_ready", "cp_copy")]
+        per = len(spans[0]) // max(args.steps, 1)
+        print("exchange trace:", [tuple(round(v[-per + i], 3) for v in spans if len(v) == len(spans[0]))
+                                  for i in range(per)], file=sys.stderr)
     _lib.device_status()
     assert torch.isfinite(result.float()).all(), "non-finite values in the block output"
 
@@ -390,6 +397,8 @@ def run_gpu(args) -> None:
     achieved = core_flops_rank / (core_ms * 1e-3) / 1e12 if core_ms else None
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
     exchange_ms, exchange_n = ktimes.pop("cp_exchange", (0.0, 0))  # a span on the exchange stream, not a kernel
+    ready_ms = ktimes.pop("cp_ready", (0.0, 0))[0]  # of which: waiting for the peers' "tiles are ready" tokens
+    copy_ms = ktimes.pop("cp_copy", (0.0, 0))[0]    # and the pulls plus the "consumed" token round
     shares = {k: round(v[0] / max(sum(t[0] for t in ktimes.values()), 1e-9), 4) for k, v in ktimes.items()}
     cores = len(os.sched_getaffinity(0))
     cpu_secs, cpu_tf = time_cpu(args.cpu_tokens, reps=1) if world == 1 and not args.no_cpu else (None, None)
@@ -438,6 +447,8 @@ def run_gpu(args) -> None:
         # context-parallel runs: time the send/receive groups spent on the exchange stream per step
         # (transfer time plus waiting for the peers; part of it overlaps the attention core)
         "cp_exchange_ms_per_step": round(exchange_ms / args.steps, 4) if world > 1 else None,
+        "cp_ready_wait_ms_per_step": round(ready_ms / args.steps, 4) if world > 1 else None,
+        "cp_copy_ms_per_step": round(copy_ms / args.steps, 4) if world > 1 else None,
         "cp_exchange_groups_per_step": exchange_n // max(args.steps, 1) if world > 1 else None,
         "kernel_time_share": shares,
         "cpu_baseline": None if cpu_tf is None else {

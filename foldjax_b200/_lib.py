@@ -261,6 +261,7 @@ SIGNATURES = {
     "b200tri_timing_enable": (C.c_int, [C.c_int32]),
     "b200tri_timing_reset": (C.c_int, []),
     "b200tri_timing_read": (C.c_int, [C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_int32)]),
+    "b200tri_timing_list": (C.c_int, [C.c_char_p, C.POINTER(C.c_double), C.c_int32, C.POINTER(C.c_int32)]),
     "b200tri_trimul_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "b200tri_trimul_workspace_bytes_dtype": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200tri_trimul_workspace_bytes_shape": (C.c_size_t, [C.c_int32] * 4),
@@ -291,6 +292,7 @@ SIGNATURES = {
                                     C.POINTER(C.c_int32)]),
     "b200tri_comm_workspace": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "b200tri_comm_pulls": (C.c_int, [C.c_void_p]),
+    "b200tri_comm_configure": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
     "b200tri_comm_group_start": (C.c_int, []),
     "b200tri_comm_group_end": (C.c_int, []),
     "b200tri_comm_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -345,7 +347,14 @@ def device_status() -> int:
 
 
 KERNELS = ("trimul_project", "trimul_contract", "trimul_finish", "triatt_project", "triatt_core", "triatt_finish",
-           "pair_transition", "pair_bias", "cp_exchange")
+           "pair_transition", "pair_bias", "cp_exchange", "cp_ready", "cp_copy")
+
+
+def kernel_time_list(name: str, capacity: int = 4096) -> list[float]:
+    """The recorded durations (ms) of one kernel name since the last timing reset, in launch order."""
+    buf, n = (C.c_double * capacity)(), C.c_int32(0)
+    check(load().b200tri_timing_list(name.encode(), buf, capacity, C.byref(n)))
+    return [buf[i] for i in range(n.value)]
 
 
 def kernel_times() -> dict[str, tuple[float, int]]:

@@ -40,6 +40,18 @@ from .triangle import _leaf
 EXCHANGE_PROBE_BYTES = 4 << 20
 
 
+#: How tiles travel between GPUs. "push" (default) / "pull": the communicator owns the exchange
+#: workspace, the peers' workspaces are mapped through CUDA IPC and the copy engines move the
+#: tiles (every sender writes into the receivers' workspaces / every receiver reads out of the
+#: owners'; NCCL only carries 4-byte tokens). "nccl": tiles are sent and received by NCCL into a
+#: workspace this module allocates.
+TRANSPORT = os.environ.get("B200TRI_CP_TRANSPORT", "push").lower()
+#: streams the copies of one exchange are spread over (1..4)
+COPY_STREAMS = int(os.environ.get("B200TRI_CP_COPY_STREAMS", "1"))
+#: SMs the attention launch that runs while key tiles travel leaves to the token kernels
+SM_RESERVE = int(os.environ.get("B200TRI_CP_SM_RESERVE", "4"))
+
+
 @dataclass
 class CPContext:
     grid: Grid
@@ -130,6 +142,7 @@ def context_parallel(cp_devices: int | None = None, layout: str | None = None, g
     handle = C.c_void_p()
     _lib.check(lib.b200tri_comm_init(C.byref(handle), raw, world, rank, grid.rows, grid.cols))
     ctx.comm = handle.value
+    _lib.check(lib.b200tri_comm_configure(handle, int(TRANSPORT != "pull"), COPY_STREAMS, SM_RESERVE))
     if verify and world > 1:
         verify_mesh_exchange(world, rank, _probe_over_comm(ctx))
     return ctx
@@ -168,11 +181,6 @@ def _ws(tag: str, nbytes: int) -> tuple[int, int]:
     return dev.aligned_ptr(raw), nbytes
 
 
-#: How tiles travel between GPUs. "pull" (default): the communicator owns the exchange workspace,
-#: the peers' workspaces are mapped through CUDA IPC and every rank copies the tiles it needs out
-#: of their owners' memory (copy engines; NCCL only carries ready / consumed tokens). "nccl": tiles
-#: are sent and received by NCCL into a workspace this module allocates.
-TRANSPORT = os.environ.get("B200TRI_CP_TRANSPORT", "pull").lower()
 
 
 def _exchange_workspace(ctx: CPContext, n: int) -> tuple[int | None, int]:
@@ -184,8 +192,8 @@ def _exchange_workspace(ctx: CPContext, n: int) -> tuple[int | None, int]:
                lib.b200tri_triatt_cp_workspace_bytes(C.c_void_p(ctx.comm), n))
     if TRANSPORT == "nccl":
         return _ws("cp_exchange", need)
-    if TRANSPORT != "pull":
-        raise ValueError(f"B200TRI_CP_TRANSPORT must be 'pull' or 'nccl', got {TRANSPORT!r}")
+    if TRANSPORT not in ("push", "pull"):
+        raise ValueError(f"B200TRI_CP_TRANSPORT must be 'push', 'pull' or 'nccl', got {TRANSPORT!r}")
     out = C.c_void_p()
     _lib.check(lib.b200tri_comm_workspace(C.c_void_p(ctx.comm), need, C.byref(out)))
     return None, 0

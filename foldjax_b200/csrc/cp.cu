@@ -21,6 +21,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <algorithm>
 #include <vector>
 
 #include "host.cuh"
@@ -29,7 +30,7 @@ struct b200tri_comm {
   ncclComm_t nccl = nullptr;
   int world = 0, rank = 0, rows = 0, cols = 0, m = 0, r = 0, c = 0, device = 0;
   cudaStream_t stream = nullptr;  // exchange stream
-  cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr;
+  cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr, ev_part[2] = {nullptr, nullptr};
   // Exchange workspace owned by the communicator (b200tri_comm_workspace) and, one process
   // per GPU, the peers' workspaces mapped into this process through CUDA IPC: tiles are then
   // pulled with device-to-device copies on the copy engines instead of NCCL's send/receive
@@ -39,6 +40,14 @@ struct b200tri_comm {
   std::vector<void*> peer_ws;  // [world], nullptr where not mapped (own rank, or no IPC)
   uint8_t* tokens = nullptr;   // device: 64-byte send slot + world x 64-byte receive slots
   bool one_process = false;    // created by b200tri_comm_init_all
+  // Copies through the mapped workspaces: written into the receiver's workspace by the sender's
+  // copy engines (push, the default: posted writes run at NVLink rate) or read out of the
+  // sender's (pull), spread over `n_copy` streams so that several copy engines work at once.
+  bool push = true;
+  int n_copy = 1;
+  int sm_reserve = 4;  // SMs left free beside a kernel that runs while tokens travel
+  cudaStream_t copy_stream[4] = {nullptr, nullptr, nullptr, nullptr};  // [0] is `stream`
+  cudaEvent_t ev_fork = nullptr, ev_join[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 
 namespace b200 {
@@ -220,12 +229,13 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
     B200_NCCL_OK(api, api->GroupEnd());
     return B200TRI_OK;
   }
-  // tokens: slot 0 is what this rank sends, slot 1 + peer what it receives from that peer
-  auto token_round = [&](bool ready) -> int {
+  // tokens: slot 0 is what this rank sends, slot 1 + peer what it receives from that peer.
+  // to_receiver = true: one token per message from its sender to its receiver; false: the reverse.
+  auto token_round = [&](bool to_receiver) -> int {
     B200_NCCL_OK(api, api->GroupStart());
     for (const Msg& msg : msgs) {
       if (!remote(msg)) continue;
-      const bool i_send = ready ? msg.src == cm->rank : msg.dst == cm->rank;
+      const bool i_send = to_receiver ? msg.src == cm->rank : msg.dst == cm->rank;
       const int peer = msg.src == cm->rank ? msg.dst : msg.src;
       if (i_send)
         B200_NCCL_OK(api, api->Send(cm->tokens, 4, ncclUint8, peer, cm->nccl, cm->stream));
@@ -235,19 +245,86 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
     B200_NCCL_OK(api, api->GroupEnd());
     return B200TRI_OK;
   };
-  int rc = token_round(true);  // every sender's tiles are complete
+  const bool push = cm->push;
+  int rc;
+  {
+    // with timing on: how long the peers were waited for
+    TimedLaunch waited(K_CP_READY, cm->stream);
+    // pull: every sender's tiles are complete. push: every receiver has reached this exchange,
+    // so nothing of its earlier work still reads the slots about to be written.
+    rc = token_round(!push);
+  }
   if (rc) return rc;
-  for (const Msg& msg : msgs) {
-    if (!remote(msg) || msg.dst != cm->rank) continue;
+  TimedLaunch copied(K_CP_COPY, cm->stream);  // ... and the copies themselves (plus the closing round)
+  if (cm->n_copy > 1) {
+    B200_CUDA_OK(cudaEventRecord(cm->ev_fork, cm->stream));
+    for (int i = 1; i < cm->n_copy; ++i) B200_CUDA_OK(cudaStreamWaitEvent(cm->copy_stream[i], cm->ev_fork, 0));
+  }
+  // Order of the copies: rounds in which every rank sends at most one tile and receives at most
+  // one (a greedy edge colouring of the whole exchange, the same on every rank, busiest ranks
+  // first). Taken in plan order instead, several senders serve the same receiver at the same
+  // time while other receivers wait, and the exchange runs at half the link rate.
+  std::vector<int> order;  // indices into msgs of the copies this rank issues, round by round
+  {
+    std::vector<int> left;
+    std::vector<int> load(2 * static_cast<size_t>(cm->world), 0);  // tiles still to send / to receive
+    for (size_t i = 0; i < msgs.size(); ++i)
+      if (want(msgs[i]) && msgs[i].src != msgs[i].dst) {
+        left.push_back(static_cast<int>(i));
+        ++load[msgs[i].src];
+        ++load[cm->world + msgs[i].dst];
+      }
+    std::vector<char> busy(2 * static_cast<size_t>(cm->world));
+    while (!left.empty()) {
+      std::fill(busy.begin(), busy.end(), 0);
+      std::stable_sort(left.begin(), left.end(), [&](int x, int y) {
+        const int lx = std::max(load[msgs[x].src], load[cm->world + msgs[x].dst]);
+        const int ly = std::max(load[msgs[y].src], load[cm->world + msgs[y].dst]);
+        return lx > ly;
+      });
+      std::vector<int> rest;
+      for (int i : left) {
+        const Msg& msg = msgs[i];
+        if (busy[msg.src] || busy[cm->world + msg.dst]) {
+          rest.push_back(i);
+          continue;
+        }
+        busy[msg.src] = busy[cm->world + msg.dst] = 1;
+        --load[msg.src];
+        --load[cm->world + msg.dst];
+        if ((push ? msg.src : msg.dst) == cm->rank) order.push_back(i);
+      }
+      left.swap(rest);
+    }
+  }
+  for (int idx : order) {
+    const Msg& msg = msgs[idx];
     send.clear();
     recv.clear();
     views(msg, true, msg.src, send);
-    views(msg, false, cm->rank, recv);
-    const uint8_t* from = static_cast<const uint8_t*>(cm->peer_ws[msg.src]);
-    for (size_t i = 0; i < send.size(); ++i)
-      B200_CUDA_OK(cudaMemcpyAsync(ws + recv[i].off, from + send[i].off, send[i].bytes, cudaMemcpyDeviceToDevice, cm->stream));
+    views(msg, false, msg.dst, recv);
+    const int peer = push ? msg.dst : msg.src;
+    uint8_t* theirs = static_cast<uint8_t*>(cm->peer_ws[peer]);
+    for (size_t i = 0; i < send.size(); ++i) {
+      const uint8_t* from = push ? ws + send[i].off : theirs + send[i].off;
+      uint8_t* to = push ? theirs + recv[i].off : ws + recv[i].off;
+      // every piece is cut into n_copy parts, one per stream: two copy engines working on one
+      // tile come closer to the link rate than one
+      const size_t part = (send[i].bytes / cm->n_copy + 1023) / 1024 * 1024;
+      for (int k = 0; k < cm->n_copy; ++k) {
+        const size_t lo = std::min(send[i].bytes, part * k), hi = std::min(send[i].bytes, part * (k + 1));
+        if (hi > lo)
+          B200_CUDA_OK(cudaMemcpyAsync(to + lo, from + lo, hi - lo, cudaMemcpyDeviceToDevice, cm->copy_stream[k]));
+      }
+    }
   }
-  return token_round(false);  // every tile has been read: the senders may reuse their buffers
+  for (int i = 1; i < cm->n_copy; ++i) {
+    B200_CUDA_OK(cudaEventRecord(cm->ev_join[i], cm->copy_stream[i]));
+    B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_join[i], 0));
+  }
+  // pull: every tile has been read, the senders may reuse their buffers. push: every tile has
+  // been written (the sender's own buffers are protected by its stream order).
+  return token_round(push);
 }
 
 int check_comm(const b200tri_comm* cm, const char* who) {
@@ -272,8 +349,15 @@ int finish_init(b200tri_comm* cm, int world, int rank, int rows, int cols) {
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_ready, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_first, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_rest, cudaEventDisableTiming));
+  for (cudaEvent_t& e : cm->ev_part) B200_CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&cm->tokens), 64 * (1 + static_cast<size_t>(world))));
   B200_CUDA_OK(cudaMemset(cm->tokens, 0, 64 * (1 + static_cast<size_t>(world))));
+  cm->copy_stream[0] = cm->stream;
+  B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_fork, cudaEventDisableTiming));
+  for (int i = 1; i < 4; ++i) {
+    B200_CUDA_OK(cudaStreamCreateWithFlags(&cm->copy_stream[i], cudaStreamNonBlocking));
+    B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_join[i], cudaEventDisableTiming));
+  }
   return B200TRI_OK;
 }
 
@@ -489,6 +573,14 @@ extern "C" int b200tri_comm_destroy(b200tri_comm* cm) {
   if (cm->ev_ready) cudaEventDestroy(cm->ev_ready);
   if (cm->ev_first) cudaEventDestroy(cm->ev_first);
   if (cm->ev_rest) cudaEventDestroy(cm->ev_rest);
+  for (cudaEvent_t e : cm->ev_part)
+    if (e) cudaEventDestroy(e);
+  if (cm->ev_fork) cudaEventDestroy(cm->ev_fork);
+  for (int i = 1; i < 4; ++i) {
+    if (cm->copy_stream[i]) cudaStreamSynchronize(cm->copy_stream[i]);
+    if (cm->ev_join[i]) cudaEventDestroy(cm->ev_join[i]);
+    if (cm->copy_stream[i]) cudaStreamDestroy(cm->copy_stream[i]);
+  }
   if (cm->stream) cudaStreamDestroy(cm->stream);
   cudaSetDevice(prev);
   delete cm;
@@ -541,8 +633,22 @@ extern "C" int b200tri_comm_workspace(b200tri_comm* cm, size_t bytes, void** out
   return B200TRI_OK;
 }
 
-// 1 if the ops called with workspace = NULL pull their tiles through mapped peer memory.
+// 1 if the ops called with workspace = NULL move their tiles through mapped peer memory.
 extern "C" int b200tri_comm_pulls(const b200tri_comm* cm) { return cm && !cm->peer_ws.empty() ? 1 : 0; }
+
+extern "C" int b200tri_comm_configure(b200tri_comm* cm, int32_t push, int32_t copy_streams, int32_t sm_reserve) {
+  int rc = check_comm(cm, "comm_configure");
+  if (rc) return rc;
+  B200_REQUIRE(copy_streams >= 1 && copy_streams <= 4, B200TRI_ERR_INVALID,
+               "comm_configure: 1 to 4 copy streams, got %d", copy_streams);
+  B200_CUDA_OK(cudaStreamSynchronize(cm->stream));  // set-up time: nothing of an exchange is in flight
+  B200_REQUIRE(sm_reserve >= 0 && sm_reserve <= 64, B200TRI_ERR_INVALID,
+               "comm_configure: 0 to 64 reserved SMs, got %d", sm_reserve);
+  cm->push = push != 0;
+  cm->n_copy = copy_streams;
+  cm->sm_reserve = sm_reserve;
+  return B200TRI_OK;
+}
 
 extern "C" int b200tri_comm_info(const b200tri_comm* cm, int32_t* world, int32_t* rank, int32_t* rows, int32_t* cols) {
   B200_REQUIRE(cm != nullptr, B200TRI_ERR_INVALID, "comm_info: null communicator");
@@ -615,7 +721,7 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   const bool incoming = a->incoming != 0;
   const TrimulPlan pl = trimul_plan(cm, d, incoming);
   // workspace = NULL: the communicator's own exchange workspace (b200tri_comm_workspace), whose
-  // peers' copies are mapped here, so tiles are pulled instead of sent
+  // peers' copies are mapped here, so tiles are copied through them instead of sent
   void* ws_ptr = a->workspace ? a->workspace : cm->ws;
   const size_t ws_have = a->workspace ? a->workspace_bytes : cm->ws_bytes;
   const bool pull = !a->workspace && !cm->peer_ws.empty();
@@ -843,8 +949,22 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   };
   if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
   B200_CUDA_OK(cudaEventRecord(cm->ev_first, cm->stream));
-  if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_KV; }, views, stream))) return rc;
-  B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
+  // The peers' key tiles travel in groups of 1, 2, 4 tiles (in the order they are walked), each
+  // fencing its own core launch: the first peer tile is computed while the next two arrive, and
+  // so on, at the price of one spill of the running state per extra launch.
+  const bool grouped = pl.n_inner % 64 == 0;
+  auto group_of = [&](const Msg& msg) {  // of a K/V message, seen from its receiver
+    const int own = starting ? msg.dst % cm->cols : msg.dst / cm->cols;
+    const int idx = (msg.slot0 - own + pl.tiles) % pl.tiles;  // position in the receiver's walk (>= 1)
+    return !grouped ? 0 : idx < 2 ? 0 : idx < 4 ? 1 : 2;
+  };
+  const int n_groups = !grouped || pl.tiles <= 2 ? 1 : pl.tiles <= 4 ? 2 : 3;
+  for (int g = 0; g < n_groups; ++g) {
+    if ((rc = post_exchange(cm, ws, pull, msgs, [&](const Msg& x) { return x.what == WHAT_KV && group_of(x) == g; },
+                            views, stream)))
+      return rc;
+    B200_CUDA_OK(cudaEventRecord(g + 1 < n_groups ? cm->ev_part[g] : cm->ev_rest, cm->stream));
+  }
 
   // key tiles: the own one first, then the peers' in rotated order (every sender serves a
   // different receiver at each position), all of them in one resumed launch
@@ -885,13 +1005,25 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   }
   B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_first, 0));
   tiles[0].unnormalized = pl.tiles > 1;
-  if ((rc = b200tri_triatt_core(&tiles[0], stream_))) return rc;
-  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+  {
+    // the peers' key tiles travel during this launch: leave their token kernels somewhere to run
+    b200::SmReserve room(pl.tiles > 1 ? cm->sm_reserve : 0);
+    if ((rc = b200tri_triatt_core(&tiles[0], stream_))) return rc;
+  }
   if (pl.tiles > 1) {
-    if (pl.n_inner % 64 == 0) {
-      tiles[1].resume = 1;
-      if ((rc = b200tri_triatt_core_multi(&tiles[1], pl.tiles - 1, stream_))) return rc;
+    if (grouped) {
+      for (int g = 0, lo = 1; g < n_groups; ++g) {
+        const int hi = std::min(pl.tiles, 2 << g);  // walk positions [lo, hi)
+        const bool last = g + 1 == n_groups;
+        B200_CUDA_OK(cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
+        tiles[lo].resume = 1;
+        tiles[lo].unnormalized = !last;
+        b200::SmReserve room(last ? 0 : cm->sm_reserve);
+        if ((rc = b200tri_triatt_core_multi(&tiles[lo], hi - lo, stream_))) return rc;
+        lo = hi;
+      }
     } else {  // ragged key tiles: one launch each, the state carried in acc_o
+      B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
       for (int idx = 1; idx < pl.tiles; ++idx) {
         tiles[idx].resume = 1;
         tiles[idx].unnormalized = idx + 1 < pl.tiles;

@@ -66,6 +66,14 @@ inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // SMs the persistent kernels of the current device may use (its SM count, or the limit
 // set for that device with b200tri_set_sm_limit).
 int sm_count();
+// While one of these lives, sm_count() on this host thread returns `keep` SMs fewer: the
+// context-parallel ops leave room beside a persistent kernel for the small NCCL kernels that
+// carry their tokens (a kernel that fills every SM would hold them back until it ends).
+struct SmReserve {
+  int before;
+  explicit SmReserve(int keep);
+  ~SmReserve();
+};
 
 // Raises a kernel's dynamic shared-memory limit, once per (kernel, device); safe to call
 // from several host threads (one per device under XLA).
@@ -85,7 +93,7 @@ int launch_linear_f32(const float* x, const float* gate, const void* w, const vo
 
 // Launch accounting and optional per-kernel event timing.
 enum KernelId { K_TRIMUL_PROJECT = 0, K_TRIMUL_CONTRACT, K_TRIMUL_FINISH, K_TRIATT_PROJECT, K_TRIATT_CORE,
-                K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_CP_EXCHANGE, K_COUNT };
+                K_TRIATT_FINISH, K_PAIR_TRANSITION, K_PAIR_BIAS, K_CP_EXCHANGE, K_CP_READY, K_CP_COPY, K_COUNT };
 void count_launch(int n = 1);
 bool timing_enabled();
 struct TimedLaunch {  // brackets the launches made during its lifetime

@@ -56,10 +56,16 @@ static int current_device_slot() {
 
 static int sm_count_device();
 
+static thread_local int t_sm_reserve = 0;
+
+SmReserve::SmReserve(int keep) : before(t_sm_reserve) { t_sm_reserve = keep > 0 ? keep : 0; }
+SmReserve::~SmReserve() { t_sm_reserve = before; }
+
 int sm_count() {
-  const int n = sm_count_device();
+  int n = sm_count_device();
   const int lim = g_sm_limit[current_device_slot()].load(std::memory_order_relaxed);
-  return (lim > 0 && lim < n) ? lim : n;
+  if (lim > 0 && lim < n) n = lim;
+  return n - t_sm_reserve > 8 ? n - t_sm_reserve : n;
 }
 
 int ensure_smem_limit(const void* kernel, int bytes) {
@@ -92,7 +98,8 @@ static std::mutex g_timing_mu;
 static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events[K_COUNT];
 static const char* const kKernelNames[K_COUNT] = {"trimul_project", "trimul_contract", "trimul_finish",
                                                   "triatt_project", "triatt_core",     "triatt_finish",
-                                                  "pair_transition", "pair_bias",      "cp_exchange"};
+                                                  "pair_transition", "pair_bias",      "cp_exchange",
+                                                  "cp_ready",        "cp_copy"};
 
 bool timing_enabled() { return g_timing[current_device_slot()].load(std::memory_order_relaxed) != 0; }
 
@@ -228,6 +235,26 @@ int b200tri_timing_read(const char* kernel, double* total_ms, int32_t* launches)
   }
   *total_ms = sum;
   *launches = static_cast<int32_t>(g_events[id].size());
+  return B200TRI_OK;
+}
+
+int b200tri_timing_list(const char* kernel, double* ms, int32_t capacity, int32_t* count) {
+  using namespace b200;
+  B200_REQUIRE(kernel && ms && count && capacity >= 0, B200TRI_ERR_INVALID, "timing_list: bad argument");
+  int id = -1;
+  for (int i = 0; i < K_COUNT; ++i)
+    if (strcmp(kernel, kKernelNames[i]) == 0) id = i;
+  B200_REQUIRE(id >= 0, B200TRI_ERR_INVALID, "timing_list: unknown kernel name '%s'", kernel);
+  B200_CUDA_OK(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lock(g_timing_mu);
+  int n = 0;
+  for (auto& e : g_events[id]) {
+    if (n >= capacity) break;
+    float t = 0.f;
+    B200_CUDA_OK(cudaEventElapsedTime(&t, e.first, e.second));
+    ms[n++] = t;
+  }
+  *count = n;
   return B200TRI_OK;
 }
 

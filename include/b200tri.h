@@ -68,8 +68,9 @@ int b200tri_selftest_wait(int64_t limit_cycles, b200tri_stream_t stream);
  *   kernels with CUDA events on the launching stream. b200tri_timing_read
  *   synchronises the device and returns, for a kernel name ("trimul_project",
  *   "trimul_contract", "trimul_finish", "triatt_project", "triatt_core",
- *   "triatt_finish", "pair_transition", "pair_bias"; "cp_exchange" = the send/receive groups of the
- *   context-parallel ops, timed on the exchange stream), the summed duration in ms and the number of launches since
+ *   "triatt_finish", "pair_transition", "pair_bias"; "cp_exchange" = the tile-exchange groups of the
+ *   context-parallel ops, timed on the exchange stream, and inside them "cp_ready" = the wait for
+ *   the peers' tiles, "cp_copy" = the copies plus the closing token round), the summed duration in ms and the number of launches since
  *   the last b200tri_timing_reset. Off by default. */
 uint64_t b200tri_launch_count(void);
 /* The persistent kernels launch one CTA per SM. b200tri_set_sm_limit(n) makes
@@ -81,6 +82,9 @@ int b200tri_set_sm_limit(int32_t sms);
 int b200tri_timing_enable(int32_t on);
 int b200tri_timing_reset(void);
 int b200tri_timing_read(const char* kernel, double* total_ms, int32_t* launches);
+/* The same records one by one, in launch order: up to `capacity` durations into ms[], their
+ * number into *count. */
+int b200tri_timing_list(const char* kernel, double* ms, int32_t capacity, int32_t* count);
 
 /* ------------------------------------------------------------------------
  * Triangle multiplicative update.
@@ -428,15 +432,22 @@ int b200tri_comm_group_end(void);
 /* Optional: an exchange workspace owned by the communicator. Collective and host-synchronous
  * (set-up time: it allocates), every rank with the same size; *ptr is the rank's workspace.
  * With one process per GPU the peers' workspaces are mapped into this process through CUDA
- * IPC, and b200tri_trimul_cp / b200tri_triatt_cp called with workspace = NULL then PULL their
- * tiles out of the owners' workspaces with device-to-device copies (copy engines at NVLink
- * rate; NCCL only carries 4-byte "ready" / "consumed" tokens) instead of receiving them from
- * NCCL's send/receive kernels. b200tri_comm_pulls() tells whether that path is active (it is
- * not when a peer could not be mapped, or under b200tri_comm_init_all: one process sees every
- * device and keeps to sends and receives). A caller-provided workspace always means sends and
- * receives. Sizes: the larger of the two *_cp_workspace_bytes. */
+ * IPC, and b200tri_trimul_cp / b200tri_triatt_cp called with workspace = NULL then move their
+ * tiles between the workspaces with device-to-device copies on the copy engines (NCCL only
+ * carries 4-byte tokens) instead of NCCL's send/receive kernels: by default every sender WRITES
+ * its tiles into the receivers' workspaces (a "slot is free" token from each receiver before, a
+ * "written" token after); b200tri_comm_configure(comm, push = 0, ...) makes every receiver READ
+ * them out of the owners' workspaces instead ("ready" before, "consumed" after), and
+ * copy_streams (1..4) spreads the copies of an exchange over that many streams; sm_reserve
+ * (default 4) is the number of SMs the attention launch that runs while key tiles travel leaves
+ * free, so that the token kernels are not held back until it ends. Every rank must configure
+ * the same direction. b200tri_comm_pulls() tells whether the mapped-memory path is
+ * active (it is not when a peer could not be mapped, or under b200tri_comm_init_all: one
+ * process sees every device and keeps to sends and receives). A caller-provided workspace
+ * always means sends and receives. Sizes: the larger of the two *_cp_workspace_bytes. */
 int b200tri_comm_workspace(b200tri_comm* comm, size_t bytes, void** ptr);
 int b200tri_comm_pulls(const b200tri_comm* comm);
+int b200tri_comm_configure(b200tri_comm* comm, int32_t push, int32_t copy_streams, int32_t sm_reserve);
 
 /* Mesh self-test, the counterpart of verify_mesh_exchange (src/foldjax/models/_cp.py:199-232):
  * every rank sends `bytes` from `shard` to every other rank and receives theirs into

@@ -35,7 +35,7 @@ def main() -> int:
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ctx = cp.context_parallel()
+    ctx = cp.context_parallel(layout=os.environ.get("CP_TEST_LAYOUT") or None)
     grid = ctx.grid
     rng = np.random.default_rng(7)
     pm_np, pa_np = trimul_params(rng, std=0.05), triatt_params(rng, std=0.05)
@@ -116,7 +116,7 @@ def main() -> int:
     ctx.close()
     dist.destroy_process_group()
     if ctx.rank == 0:
-        print(f"transport: {'pull' if pulls else 'nccl'}", flush=True)
+        print(f"transport: {cp.TRANSPORT if pulls else 'nccl'}", flush=True)
         print("CP_WORKER_OK" if flag.item() == 0 else "CP_WORKER_FAILED", flush=True)
     return int(flag.item() != 0)
 

@@ -16,10 +16,11 @@ torch = pytest.importorskip("torch")
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def _run(world: int, tokens: int, transport: str = "pull") -> str:
+def _run(world: int, tokens: int, transport: str = "push", layout: str = "") -> str:
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0", B200TRI_CP_TRANSPORT=transport)
+    env = dict(os.environ, CP_TEST_TOKENS=str(tokens), NCCL_NVLS_ENABLE="0", B200TRI_CP_TRANSPORT=transport,
+               CP_TEST_LAYOUT=layout)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(ROOT / "tests" / "cp_worker.py")]
     done = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900)
@@ -30,8 +31,24 @@ def _run(world: int, tokens: int, transport: str = "pull") -> str:
 @pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (2, 256), (4, 512), (4, 256), (8, 1024), (8, 256),
                                           (8, 3072)])
 def test_context_parallel_matches_single_gpu(world, tokens):
-    """Tiles pulled out of the peers' mapped workspaces (the default transport)."""
+    """Tiles written into the peers' mapped workspaces by the senders (the default transport)."""
     out = _run(world, tokens)
+    assert "transport: push" in out, out[-2000:]
+    print(out)
+
+
+@pytest.mark.parametrize("world,tokens", [(4, 512), (4, 1024)])
+def test_context_parallel_on_a_one_row_grid(world, tokens):
+    """1 x 4: four key tiles per row, so the peers' tiles arrive and are computed in groups."""
+    out = _run(world, tokens, layout="1x4")
+    assert "transport: push" in out, out[-2000:]
+    print(out)
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 256), (4, 512), (8, 1024)])
+def test_context_parallel_pulling_tiles(world, tokens):
+    """The same ops with every receiver reading its tiles out of the owners' mapped workspaces."""
+    out = _run(world, tokens, transport="pull")
     assert "transport: pull" in out, out[-2000:]
     print(out)
 

@@ -375,11 +375,22 @@ def test_core_walks_several_key_tiles_in_one_launch(cuda_device):
     two = torch.full_like(ref, float("nan"))
     launch([tile_args(tiles[1], n_kt, o=two.data_ptr(), unnormalized=1, **state)])  # "own" tile first
     launch([tile_args(sl, n_kt, o=two.data_ptr(), resume=1, **state) for sl in (tiles[2], tiles[0])])
+    # the grouped pattern of a four-tile ring: own tile, then one tile, then two tiles in a launch
+    # that resumes AND leaves the state unnormalised in the middle (64-key tiles here)
+    n_q4 = n_k // 6
+    quarter = [slice(t * n_q4, (t + 1) * n_q4) for t in range(6)]
+    three = torch.full_like(ref, float("nan"))
+    acc.zero_(); rmax.zero_(); rsum.zero_()
+    launch([tile_args(quarter[2], n_q4, o=three.data_ptr(), unnormalized=1, **state)])
+    launch([tile_args(quarter[3], n_q4, o=three.data_ptr(), resume=1, unnormalized=1, **state)])
+    launch([tile_args(sl, n_q4, o=three.data_ptr(), resume=1, unnormalized=1, **state) for sl in (quarter[4], quarter[5])])
+    launch([tile_args(sl, n_q4, o=three.data_ptr(), resume=1, **state) for sl in (quarter[0], quarter[1])])
     torch.cuda.synchronize()
     _lib.device_status()
     r = ref.float().cpu().numpy()
     print(assert_parity(r, one.float().cpu().numpy(), label="three key tiles, one launch", mean_tol=2e-4))
     print(assert_parity(r, two.float().cpu().numpy(), label="own tile + resumed multi-tile launch", mean_tol=2e-4))
+    print(assert_parity(r, three.float().cpu().numpy(), label="own tile + grouped resumed launches", mean_tol=2e-4))
     # too many tiles, or ragged tiles, are refused
     bad = (_lib.TriattCoreArgs * 8)()
     assert lib.b200tri_triatt_core_multi(bad, 8, None) == _lib.ERR_INVALID
