@@ -297,6 +297,7 @@ SIGNATURES = {
     "b200tri_comm_group_end": (C.c_int, []),
     "b200tri_comm_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200tri_cp_plan": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(CpMsg), C.c_int32]),
+    "b200tri_cp_rounds": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32]),
     "b200tri_trimul_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),
     "b200tri_trimul_cp": (C.c_int, [C.c_void_p, C.POINTER(TrimulCpArgs), C.c_void_p]),
     "b200tri_triatt_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),

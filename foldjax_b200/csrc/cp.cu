@@ -180,6 +180,53 @@ struct Offsets {
   size_t total() const { return (off + 1023) / 1024 * 1024; }
 };
 
+// Round of every message of an exchange (-1: not wanted, or local). In one round every rank
+// sends at most one tile and receives at most one, and there are no more rounds than the busiest
+// rank has messages: an edge colouring of the bipartite sender/receiver graph (alternating-path
+// recolouring), identical on every rank. Copies issued in this order keep every link busy
+// without several senders serving the same receiver at the same time. `big` messages are coloured
+// first, so they share the early rounds.
+template <typename Want, typename Big>
+std::vector<int> copy_rounds(const std::vector<Msg>& msgs, int world, Want want, Big big) {
+  std::vector<int> round(msgs.size(), -1), edges;
+  std::vector<int> deg(2 * static_cast<size_t>(world), 0);
+  for (int pass = 0; pass < 2; ++pass)
+    for (size_t i = 0; i < msgs.size(); ++i)
+      if (want(msgs[i]) && msgs[i].src != msgs[i].dst && big(msgs[i]) == (pass == 0)) {
+        edges.push_back(static_cast<int>(i));
+        ++deg[msgs[i].src];
+        ++deg[world + msgs[i].dst];
+      }
+  const int colours = edges.empty() ? 0 : *std::max_element(deg.begin(), deg.end());
+  // at[node][colour] = message holding that colour at the node (senders 0..world, receivers after)
+  std::vector<std::vector<int>> at(2 * static_cast<size_t>(world), std::vector<int>(colours, -1));
+  auto free_at = [&](int node) {
+    int c = 0;
+    while (at[node][c] >= 0) ++c;  // a node has at most `colours` messages, this one not yet placed
+    return c;
+  };
+  for (int e : edges) {
+    const int u = msgs[e].src, v = world + msgs[e].dst;
+    const int a = free_at(u), b = free_at(v);
+    if (at[v][a] >= 0) {  // a is taken at the receiver: swap a and b along the path that starts there
+      std::vector<int> path;
+      for (int node = v, c = a; at[node][c] >= 0; c = c == a ? b : a) {
+        const int f = at[node][c];
+        path.push_back(f);
+        node = node >= world ? msgs[f].src : world + msgs[f].dst;
+      }
+      for (int f : path) at[msgs[f].src][round[f]] = at[world + msgs[f].dst][round[f]] = -1;
+      for (int f : path) {
+        round[f] = round[f] == a ? b : a;
+        at[msgs[f].src][round[f]] = at[world + msgs[f].dst][round[f]] = f;
+      }
+    }
+    round[e] = a;
+    at[u][a] = at[v][a] = e;
+  }
+  return round;
+}
+
 // Post this rank's share of `msgs` (those accepted by `want`). `views(msg, send, who, out)`
 // lists the pieces of a message as offsets into the workspace: on the send side inside the
 // workspace of rank `who` = msg.src, on the receive side inside this rank's. Local messages
@@ -191,7 +238,8 @@ struct Offsets {
 //    "consumed" token back after them, so a sender never overwrites a tile that is being read.
 template <typename Want, typename Views>
 int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Msg>& msgs, Want want, Views views,
-                  cudaStream_t compute) {
+                  cudaStream_t compute, int wide_what = -1) {
+  auto big = [&](const Msg& msg) { return msg.what == wide_what; };  // messages larger than the others
   const Nccl* api = nccl_api();
   B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
   std::vector<Piece> send, recv;
@@ -266,36 +314,12 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
   // time while other receivers wait, and the exchange runs at half the link rate.
   std::vector<int> order;  // indices into msgs of the copies this rank issues, round by round
   {
-    std::vector<int> left;
-    std::vector<int> load(2 * static_cast<size_t>(cm->world), 0);  // tiles still to send / to receive
-    for (size_t i = 0; i < msgs.size(); ++i)
-      if (want(msgs[i]) && msgs[i].src != msgs[i].dst) {
-        left.push_back(static_cast<int>(i));
-        ++load[msgs[i].src];
-        ++load[cm->world + msgs[i].dst];
-      }
-    std::vector<char> busy(2 * static_cast<size_t>(cm->world));
-    while (!left.empty()) {
-      std::fill(busy.begin(), busy.end(), 0);
-      std::stable_sort(left.begin(), left.end(), [&](int x, int y) {
-        const int lx = std::max(load[msgs[x].src], load[cm->world + msgs[x].dst]);
-        const int ly = std::max(load[msgs[y].src], load[cm->world + msgs[y].dst]);
-        return lx > ly;
-      });
-      std::vector<int> rest;
-      for (int i : left) {
-        const Msg& msg = msgs[i];
-        if (busy[msg.src] || busy[cm->world + msg.dst]) {
-          rest.push_back(i);
-          continue;
-        }
-        busy[msg.src] = busy[cm->world + msg.dst] = 1;
-        --load[msg.src];
-        --load[cm->world + msg.dst];
-        if ((push ? msg.src : msg.dst) == cm->rank) order.push_back(i);
-      }
-      left.swap(rest);
-    }
+    const std::vector<int> round = copy_rounds(msgs, cm->world, want, big);
+    int n_rounds = 0;
+    for (int r : round) n_rounds = std::max(n_rounds, r + 1);
+    for (int r = 0; r < n_rounds; ++r)
+      for (size_t i = 0; i < msgs.size(); ++i)
+        if (round[i] == r && (push ? msgs[i].src : msgs[i].dst) == cm->rank) order.push_back(static_cast<int>(i));
   }
   for (int idx : order) {
     const Msg& msg = msgs[idx];
@@ -497,6 +521,23 @@ extern "C" int b200tri_cp_plan(int32_t rows, int32_t cols, int32_t op, b200tri_c
   if (out)
     for (size_t i = 0; i < msgs.size() && static_cast<int32_t>(i) < capacity; ++i) out[i] = msgs[i];
   return static_cast<int>(msgs.size());
+}
+
+extern "C" int b200tri_cp_rounds(int32_t rows, int32_t cols, int32_t op, int32_t what, int32_t* round, int32_t capacity) {
+  if (check_grid(rows * cols, rows, cols)) return -1;
+  if (op < B200TRI_CP_TRIMUL_OUTGOING || op > B200TRI_CP_TRIATT_ENDING) {
+    set_error("cp_rounds: unknown op %d", op);
+    return -1;
+  }
+  const std::vector<Msg> msgs = build_plan(Grid{rows, cols, cols / rows}, op);
+  // the tile of an outgoing tri-mult `a` message spans cols / rows blocks, every other message one
+  const bool wide = op == B200TRI_CP_TRIMUL_OUTGOING && cols > rows;
+  const std::vector<int> r = copy_rounds(
+      msgs, rows * cols, [&](const Msg& m) { return what < 0 || m.what == what; },
+      [&](const Msg& m) { return wide && m.what == WHAT_A; });
+  if (round)
+    for (size_t i = 0; i < r.size() && static_cast<int32_t>(i) < capacity; ++i) round[i] = r[i];
+  return static_cast<int>(r.size());
 }
 
 extern "C" int b200tri_comm_unique_id(void* id128) {
@@ -797,7 +838,7 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
             out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
         }
       },
-      stream);
+      stream, !incoming && m > 1 ? WHAT_A : -1);
   if (rc) return rc;
   B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
   B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));

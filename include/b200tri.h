@@ -464,6 +464,12 @@ enum { B200TRI_CP_TRIMUL_OUTGOING = 0, B200TRI_CP_TRIMUL_INCOMING = 1, B200TRI_C
        B200TRI_CP_TRIATT_ENDING = 3 };
 typedef struct { int32_t src, dst, what, block, slot0, slot1; } b200tri_cp_msg;
 int b200tri_cp_plan(int32_t rows, int32_t cols, int32_t op, b200tri_cp_msg* out, int32_t capacity);
+/* Order of the copies of one exchange: round[i] for message i of b200tri_cp_plan (-1 for a
+ * local message or one whose `what` differs from the filter; what < 0 takes all). Within a
+ * round every rank sends at most one tile and receives at most one; the ops issue their copies
+ * round by round. Returns the number of messages, or -1 on a bad grid / op. No counterpart in
+ * the reference, whose ring hops are scheduled by XLA. */
+int b200tri_cp_rounds(int32_t rows, int32_t cols, int32_t op, int32_t what, int32_t* round, int32_t capacity);
 
 /* Triangle multiplication on this rank's tile. x / residual / out are the rank's tile
  * [n / rows][n / cols][128] bf16; mask is the WHOLE [n][n] float32 mask (or NULL), replicated

@@ -13,6 +13,7 @@ exchange schedule the library executes.
 
 from __future__ import annotations
 
+import ctypes as C
 import os
 import sys
 from pathlib import Path
@@ -47,6 +48,39 @@ def test_library_schedule_equals_the_python_plan(rows, cols):
             slot = tuple(want.slot) + (0,) * (2 - len(want.slot))
             assert (got.src, got.dst, got.what, got.block, got.slot0, got.slot1) == (
                 want.src, want.dst, what[want.what], -1 if want.block is None else want.block, slot[0], slot[1])
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 2), (2, 2), (2, 4), (3, 3), (1, 4), (2, 6), (4, 4)])
+def test_copy_rounds_are_contention_free(rows, cols):
+    """The order in which the ops issue their copies: every remote message gets exactly one
+    round, local ones none; in a round no rank sends twice or receives twice; and the number of
+    rounds equals the busiest rank's message count, the lower bound."""
+    from foldjax_b200 import _lib
+
+    lib = _lib.load()
+    for op in (_lib.CP_TRIMUL_OUTGOING, _lib.CP_TRIMUL_INCOMING, _lib.CP_TRIATT_STARTING, _lib.CP_TRIATT_ENDING):
+        count = lib.b200tri_cp_plan(rows, cols, op, None, 0)
+        msgs = (_lib.CpMsg * count)()
+        lib.b200tri_cp_plan(rows, cols, op, msgs, count)
+        for what in ((-1,) if op in (_lib.CP_TRIMUL_OUTGOING, _lib.CP_TRIMUL_INCOMING) else (2, 3)):
+            rounds = (C.c_int32 * count)()
+            assert lib.b200tri_cp_rounds(rows, cols, op, what, rounds, count) == count
+            seen: dict[int, tuple[set, set]] = {}
+            load: dict[tuple[str, int], int] = {}
+            for m, r in zip(msgs, rounds):
+                wanted = (what < 0 or m.what == what) and m.src != m.dst
+                assert (r >= 0) == wanted
+                if not wanted:
+                    continue
+                senders, receivers = seen.setdefault(r, (set(), set()))
+                assert m.src not in senders and m.dst not in receivers, (rows, cols, op, r)
+                senders.add(m.src)
+                receivers.add(m.dst)
+                load[("s", m.src)] = load.get(("s", m.src), 0) + 1
+                load[("r", m.dst)] = load.get(("r", m.dst), 0) + 1
+            if load:
+                assert sorted(seen) == list(range(len(seen)))
+                assert len(seen) == max(load.values()), (rows, cols, op, len(seen), max(load.values()))
 
 
 def test_library_refuses_grids_it_cannot_tile():
