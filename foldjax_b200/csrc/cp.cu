@@ -30,7 +30,8 @@ struct b200tri_comm {
   ncclComm_t nccl = nullptr;
   int world = 0, rank = 0, rows = 0, cols = 0, m = 0, r = 0, c = 0, device = 0;
   cudaStream_t stream = nullptr;  // exchange stream
-  cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr, ev_part[2] = {nullptr, nullptr};
+  cudaEvent_t ev_ready = nullptr, ev_first = nullptr, ev_rest = nullptr;
+  std::vector<cudaEvent_t> ev_part;  // fences of the groups of one exchange but the last: max(3, world) of them
   // Exchange workspace owned by the communicator (b200tri_comm_workspace) and, one process
   // per GPU, the peers' workspaces mapped into this process through CUDA IPC: tiles are then
   // pulled with device-to-device copies on the copy engines instead of NCCL's send/receive
@@ -373,6 +374,7 @@ int finish_init(b200tri_comm* cm, int world, int rank, int rows, int cols) {
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_ready, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_first, cudaEventDisableTiming));
   B200_CUDA_OK(cudaEventCreateWithFlags(&cm->ev_rest, cudaEventDisableTiming));
+  cm->ev_part.assign(world > 3 ? world : 3, nullptr);
   for (cudaEvent_t& e : cm->ev_part) B200_CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   B200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&cm->tokens), 64 * (1 + static_cast<size_t>(world))));
   B200_CUDA_OK(cudaMemset(cm->tokens, 0, 64 * (1 + static_cast<size_t>(world))));
@@ -804,99 +806,117 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   pa.workspace_bytes = b200tri_trimul_project_workspace_bytes();
   if ((rc = b200tri_trimul_project(&pa, stream_))) return rc;
 
-  // exchange: ordered after the projection, the contraction ordered after it
+  // Exchange and contraction, in row chunks: the output rows of the tile are cut into G chunks
+  // (k_split per n_c-row block); group g of the exchange carries chunk g of every `a` message
+  // (group 0 all `b` messages as well) and fences the contraction of output chunk g alone, so all
+  // but the last chunk are contracted while later groups travel. Channel-major data sits in
+  // 64-row blocks of rb_bytes each, so a row chunk of a message is one contiguous piece.
   const size_t blk_bytes = pl.blk * 2;
+  int k_split = 1;
+  if (cm->world > 1 && pl.rpb == 64)
+    for (k_split = m >= 4 ? 1 : 4 / m; k_split > 1 && (n_c % k_split || (n_c / k_split) % 128); k_split /= 2) {
+    }
+  const int G = m * k_split;
+  const int64_t h = n_c / k_split;  // rows per chunk
+  const size_t rb_bytes = static_cast<size_t>(128) * 64 * pl.ld * 2;
+  auto chunk_off = [&](int q) { return k_split > 1 ? static_cast<size_t>(q * h / 64) * rb_bytes : 0; };
+  const size_t chunk_bytes = k_split > 1 ? static_cast<size_t>(h / 64) * rb_bytes : blk_bytes;
   B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
   B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
   const std::vector<Msg> msgs =
       build_plan(Grid{cm->rows, cm->cols, m}, incoming ? B200TRI_CP_TRIMUL_INCOMING : B200TRI_CP_TRIMUL_OUTGOING);
-  rc = post_exchange(
-      cm, ws, pull, msgs, [](const Msg&) { return true; },
-      [&](const Msg& msg, bool send, int who, std::vector<Piece>& out) {
-        if (send) {  // the local arrays of rank `who`: the same layout, its own slot positions
-          const int wr = who / cm->cols, wc = who % cm->cols;
-          const size_t a_loc = incoming ? pl.a_loc : pl.a_all + blk_bytes * m * wc;
-          const size_t b_loc = incoming ? pl.b_all + blk_bytes * wr : pl.b_loc;
-          const size_t src = msg.what == WHAT_A ? a_loc : b_loc;
-          if (msg.block < 0) {  // a whole local array: m blocks (outgoing a), or one block
-            const size_t whole = (!incoming && msg.what == WHAT_A) ? blk_bytes * m : blk_bytes;
-            out.push_back({src, whole});
-          } else {
-            out.push_back({src + blk_bytes * msg.block, blk_bytes});
+  for (int g = 0; g < G; ++g) {
+    const int s = g / k_split, q = g % k_split;  // n_c-row block and chunk inside it
+    rc = post_exchange(
+        cm, ws, pull, msgs,
+        [&](const Msg& msg) { return msg.what == WHAT_B ? g == 0 : (!incoming || msg.slot0 == s); },
+        [&](const Msg& msg, bool send, int who, std::vector<Piece>& out) {
+          if (msg.what == WHAT_B) {
+            if (send) {
+              const size_t b_loc = incoming ? pl.b_all + blk_bytes * (who / cm->cols) : pl.b_loc;
+              out.push_back({b_loc + (msg.block < 0 ? 0 : blk_bytes * msg.block), blk_bytes});
+            } else {
+              out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+            }
+            return;
           }
-          return;
-        }
-        if (!incoming) {
-          if (msg.what == WHAT_A)
-            out.push_back({pl.a_all + blk_bytes * m * msg.slot0, blk_bytes * m});
+          // `a`: the sender's local array has the receiver slot's layout; outgoing messages span
+          // the m blocks of the tile (chunk g of all its rows), incoming ones one block (chunk q)
+          size_t base;
+          if (!incoming)
+            base = pl.a_all + blk_bytes * m * (send ? who % cm->cols : msg.slot0) + blk_bytes * s;
           else
-            out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
-        } else {
-          if (msg.what == WHAT_A)
-            out.push_back({pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1), blk_bytes});
-          else
-            out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
-        }
-      },
-      stream, !incoming && m > 1 ? WHAT_A : -1);
-  if (rc) return rc;
-  B200_CUDA_OK(cudaEventRecord(cm->ev_rest, cm->stream));
-  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+            base = send ? pl.a_loc : pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1);
+          out.push_back({base + chunk_off(q), chunk_bytes});
+        },
+        stream, g == 0 && chunk_bytes < blk_bytes ? WHAT_B : -1);
+    if (rc) return rc;
+    B200_CUDA_OK(cudaEventRecord(g + 1 < G ? cm->ev_part[g] : cm->ev_rest, cm->stream));
+  }
 
-  // one contraction launch per output row block walks all k-sources (fp32 accumulation on chip)
+  // one contraction launch per output chunk walks all k-sources (fp32 accumulation on chip)
   const int64_t t_chan = static_cast<int64_t>(pl.t_rpb) * pl.ldt;
   const int64_t t_row = pl.rpb == 64 ? static_cast<int64_t>(128) * pl.ldt : pl.ldt;
-  for (int s = 0; s < m; ++s) {
+  for (int g = 0; g < G; ++g) {
+    const int s = g / k_split, q = g % k_split;
+    const bool last = g + 1 == G;
+    B200_CUDA_OK(cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
     b200tri_trimul_contract_args ca = {};
-    ca.n_i = ca.n_j = static_cast<int32_t>(n_c);
+    ca.n_i = static_cast<int32_t>(h);
+    ca.n_j = static_cast<int32_t>(n_c);
     ca.n_k = pl.n_k;
     ca.n_src = pl.n_src;
     if (!incoming) {
-      ca.a = ws + pl.a_all + blk_bytes * s;
+      ca.a = ws + pl.a_all + blk_bytes * s + chunk_off(q);
       ca.a_src_stride = static_cast<int64_t>(pl.blk) * m;
     } else {
-      ca.a = ws + pl.a_all + blk_bytes * (static_cast<size_t>(s) * cm->rows);
+      ca.a = ws + pl.a_all + blk_bytes * (static_cast<size_t>(s) * cm->rows) + chunk_off(q);
       ca.a_src_stride = static_cast<int64_t>(pl.blk);
     }
     ca.b = ws + pl.b_all;
     ca.b_src_stride = static_cast<int64_t>(pl.blk);
     ca.a_ld = ca.b_ld = pl.ld;
     ca.a_chan_stride = ca.b_chan_stride = static_cast<int64_t>(pl.rpb) * pl.ld;
-    ca.out_bf16 = ws + pl.t + static_cast<size_t>(2) * s * n_c * t_row;
+    ca.out_bf16 = ws + pl.t + static_cast<size_t>(2) * (static_cast<size_t>(s) * n_c + static_cast<size_t>(q) * h) * t_row;
     ca.out_ld = pl.ldt;
     ca.out_chan_stride = t_chan;
     ca.a_rows_per_block = ca.b_rows_per_block = pl.rpb;
     ca.out_rows_per_block = pl.t_rpb;
     ca.a_block_stride = ca.b_block_stride = static_cast<int64_t>(128) * pl.rpb * pl.ld;
     ca.out_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
+    // later groups travel during these launches: leave their token kernels somewhere to run
+    b200::SmReserve room(last ? 0 : cm->sm_reserve);
     if ((rc = b200tri_trimul_contract(&ca, stream_))) return rc;
-  }
 
-  b200tri_trimul_finish_args fa = {};
-  fa.n_i = static_cast<int32_t>(n_r);
-  fa.n_j = static_cast<int32_t>(n_c);
-  fa.eps = a->eps;
-  fa.t = ws + pl.t;
-  fa.t_ld = pl.ldt;
-  fa.t_chan_stride = t_chan;
-  fa.t_rows_per_block = pl.t_rpb;
-  fa.t_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
-  fa.x = a->x;
-  fa.xs_i = n_c * 128;
-  fa.xs_j = 128;
-  fa.norm_in_scale = a->norm_in_scale;
-  fa.norm_in_bias = a->norm_in_bias;
-  fa.norm_out_scale = a->norm_out_scale;
-  fa.norm_out_bias = a->norm_out_bias;
-  fa.p_out = a->p_out;
-  fa.g_out = a->g_out;
-  fa.residual = a->residual;
-  fa.out = a->out;
-  fa.os_i = n_c * 128;
-  fa.os_j = 128;
-  fa.workspace = ws + pl.fin;
-  fa.workspace_bytes = b200tri_trimul_finish_workspace_bytes();
-  return b200tri_trimul_finish(&fa, stream_);
+    // output stage of the same rows (row-local)
+    const int64_t row0 = static_cast<int64_t>(s) * n_c + static_cast<int64_t>(q) * h;
+    b200tri_trimul_finish_args fa = {};
+    fa.n_i = static_cast<int32_t>(h);
+    fa.n_j = static_cast<int32_t>(n_c);
+    fa.eps = a->eps;
+    fa.t = ws + pl.t + static_cast<size_t>(2) * row0 * t_row;
+    fa.t_ld = pl.ldt;
+    fa.t_chan_stride = t_chan;
+    fa.t_rows_per_block = pl.t_rpb;
+    fa.t_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
+    fa.x = static_cast<const uint8_t*>(a->x) + static_cast<size_t>(2) * row0 * n_c * 128;
+    fa.xs_i = n_c * 128;
+    fa.xs_j = 128;
+    fa.norm_in_scale = a->norm_in_scale;
+    fa.norm_in_bias = a->norm_in_bias;
+    fa.norm_out_scale = a->norm_out_scale;
+    fa.norm_out_bias = a->norm_out_bias;
+    fa.p_out = a->p_out;
+    fa.g_out = a->g_out;
+    fa.residual = a->residual ? static_cast<const uint8_t*>(a->residual) + static_cast<size_t>(2) * row0 * n_c * 128 : nullptr;
+    fa.out = static_cast<uint8_t*>(a->out) + static_cast<size_t>(2) * row0 * n_c * 128;
+    fa.os_i = n_c * 128;
+    fa.os_j = 128;
+    fa.workspace = ws + pl.fin;
+    fa.workspace_bytes = b200tri_trimul_finish_workspace_bytes();
+    if ((rc = b200tri_trimul_finish(&fa, stream_))) return rc;
+  }
+  return B200TRI_OK;
 }
 
 // ---------------------------------------------------------------------------- tri-attn
