@@ -77,3 +77,86 @@ def triangle_block_forward(params: Mapping[str, Any], z: Any, mask: Any | None, 
         torch.cuda.current_stream().synchronize()
     dev.check_device_status()  # raises if a kernel of the block gave up on a bounded wait
     return out
+
+
+def stream_host_blocks(run_block, items, outs=None):
+    """Run ``run_block(z_device, mask_device) -> z_device`` over a sequence of HOST inputs
+    with the transfers overlapped: while the kernels of item k run, item k+1 is copied to
+    the GPU and the result of item k-1 is copied back (three streams, two device input slots,
+    PCIe in both directions at once).
+
+    ``items``: a sequence of ``(z, mask)`` CPU torch tensors, bf16 ``z`` and float32 ``mask``
+    (or None), all of one shape; pinned memory lets the copies run asynchronously. ``outs``:
+    optional list of pinned CPU bf16 tensors to receive the results (allocated if None).
+    Returns the list of outputs after everything has finished. This is the end-to-end form
+    for a stream of complexes (or of trunk recycles whose inputs live on the host); a single
+    call of ``triangle_block_forward`` on host arrays cannot overlap its own two copies with
+    anything, because the first op needs the whole pair tensor and the last one produces it.
+    """
+    items = list(items)
+    if not items:
+        return []
+    for z, mask in items:
+        if not (isinstance(z, torch.Tensor) and not z.is_cuda and z.dtype == torch.bfloat16 and z.is_contiguous()):
+            raise ValueError("stream_host_blocks takes contiguous CPU bfloat16 tensors for z")
+        if z.shape != items[0][0].shape:
+            raise ValueError("stream_host_blocks: every item must have the same shape")
+        if mask is not None and not (isinstance(mask, torch.Tensor) and not mask.is_cuda and mask.dtype == torch.float32):
+            raise ValueError("stream_host_blocks takes CPU float32 tensors (or None) for mask")
+    if outs is None:
+        dev.require_cuda()
+        outs = [torch.empty(z.shape, dtype=torch.bfloat16, pin_memory=True) for z, _ in items]
+    if len(outs) != len(items):
+        raise ValueError(f"stream_host_blocks: {len(items)} items but {len(outs)} output buffers")
+    for o, (z, _) in zip(outs, items):
+        if not (isinstance(o, torch.Tensor) and not o.is_cuda and o.dtype == torch.bfloat16 and o.is_contiguous()
+                and o.shape == z.shape):
+            raise ValueError("stream_host_blocks: outputs must be contiguous CPU bfloat16 tensors of the inputs' shape")
+    dev.require_cuda()
+    compute = torch.cuda.current_stream()
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    z0, m0 = items[0]
+    z_slot = [torch.empty(z0.shape, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    m_slot = [None if m0 is None else torch.empty(m0.shape, dtype=torch.float32, device="cuda") for _ in range(2)]
+    loaded = [torch.cuda.Event() for _ in range(2)]     # slot filled (copy_in)
+    consumed = [torch.cuda.Event() for _ in range(2)]   # slot no longer read (compute)
+    start = torch.cuda.Event()
+    start.record(compute)
+    copy_in.wait_event(start)   # nothing of this call overtakes the caller's earlier work
+    copy_out.wait_event(start)
+    for k, (z, mask) in enumerate(items):
+        slot = k & 1
+        with torch.cuda.stream(copy_in):
+            if k >= 2:
+                copy_in.wait_event(consumed[slot])
+            z_slot[slot].copy_(z, non_blocking=True)
+            if mask is not None:
+                m_slot[slot].copy_(mask, non_blocking=True)
+            loaded[slot].record(copy_in)
+        compute.wait_event(loaded[slot])
+        # the block writes its own work buffers; the input slot is free once its last reader ran
+        res = run_block(z_slot[slot], m_slot[slot])
+        if res.data_ptr() == z_slot[slot].data_ptr():
+            raise RuntimeError("run_block must not return its input buffer")
+        done = torch.cuda.Event()
+        done.record(compute)
+        consumed[slot].record(compute)
+        res.record_stream(copy_out)  # the allocator may not reuse it before the copy below has run
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            outs[k].copy_(res, non_blocking=True)
+        del res
+    finish = torch.cuda.Event()
+    finish.record(copy_out)
+    compute.wait_event(finish)
+    copy_in.synchronize()
+    copy_out.synchronize()
+    compute.synchronize()
+    dev.check_device_status()
+    return outs
+
+
+def triangle_block_forward_stream(params: Mapping[str, Any], items, outs=None):
+    """``triangle_block_forward`` over a sequence of host ``(z, mask)`` pairs with the copies of
+    neighbouring items overlapped with the kernels (see ``stream_host_blocks``)."""
+    return stream_host_blocks(lambda zd, md: triangle_block_forward(params, zd, md), items, outs)

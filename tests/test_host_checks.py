@@ -53,3 +53,22 @@ def test_workspace_reuse_accounts_for_the_alignment_slack(monkeypatch):
     b = dev.workspace(4097, "t")  # 4097 + 1024 > 5120: the old buffer no longer covers it
     assert b is not a and b.numel() == 4097 + 1024
     dev.release_workspaces()
+
+
+def test_streamed_blocks_refuse_mismatched_host_buffers():
+    """stream_host_blocks checks its host buffers before it touches a device."""
+    from foldjax_b200.block import stream_host_blocks
+
+    z = torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16)
+    run = lambda zd, md: zd + 1  # never reached
+    assert stream_host_blocks(run, []) == []
+    with pytest.raises(ValueError, match="bfloat16"):
+        stream_host_blocks(run, [(z.float(), None)], [z.clone()])
+    with pytest.raises(ValueError, match="same shape"):
+        stream_host_blocks(run, [(z, None), (z[:, :4].contiguous(), None)], [z.clone(), z.clone()])
+    with pytest.raises(ValueError, match="float32"):
+        stream_host_blocks(run, [(z, torch.ones(1, 8, 8, dtype=torch.float64))], [z.clone()])
+    with pytest.raises(ValueError, match="1 items but 2"):
+        stream_host_blocks(run, [(z, None)], [z.clone(), z.clone()])
+    with pytest.raises(ValueError, match="outputs must be"):
+        stream_host_blocks(run, [(z, None)], [z.float()])

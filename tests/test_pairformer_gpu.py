@@ -94,6 +94,31 @@ def test_pair_track_only_equals_the_per_op_block(cuda_device):
     assert torch.equal(z_one, triangle_block_forward(pd, zd, pmd))
 
 
+def test_streamed_host_blocks_equal_one_call_each(cuda_device):
+    """stream_host_blocks (copies of neighbouring items overlapped with the kernels) gives, item
+    by item, exactly what triangle_block_forward gives for that item alone; five different
+    items, so both device slots are reused while their neighbours are still in flight."""
+    from foldjax_b200 import _device as dev
+    from foldjax_b200.block import triangle_block_forward, triangle_block_forward_stream
+
+    params, _, z, _, pair_mask = _case(11, 136, 5)
+    pd = dev.params_to_device(params)
+    gen = torch.Generator().manual_seed(3)
+    items = []
+    for k in range(5):
+        zk = (torch.from_numpy(z).float() + 0.25 * k * torch.randn(z.shape, generator=gen)).bfloat16().pin_memory()
+        mk = torch.from_numpy(pair_mask).float().clone()
+        if k % 2:
+            mk[:, :, : 3 + k] = 0.0
+        items.append((zk, mk.pin_memory()))
+    outs = triangle_block_forward_stream(pd, items)
+    assert len(outs) == 5
+    for (zk, mk), got in zip(items, outs):
+        want = triangle_block_forward(pd, zk.cuda(), mk.cuda()).cpu()
+        assert torch.equal(got, want)
+    assert not torch.equal(outs[0], outs[2])
+
+
 def test_bad_arguments_are_rejected(cuda_device):
     from foldjax_b200 import _lib
     from foldjax_b200.pairformer import pairformer_forward, pairformer_layer_forward
