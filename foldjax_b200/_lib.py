@@ -136,7 +136,7 @@ class PairTransitionArgs(C.Structure):
         ("x", C.c_void_p), ("norm_scale", C.c_void_p), ("norm_bias", C.c_void_p),
         ("fc1", C.c_void_p), ("fc2", C.c_void_p), ("fc3", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("row_mask", C.c_void_p),
     ]
 
 
@@ -218,6 +218,7 @@ class PairformerArgs(C.Structure):
         ("z_in", C.c_void_p), ("z_out", C.c_void_p), ("s_in", C.c_void_p), ("s_out", C.c_void_p),
         ("pair_mask", C.c_void_p), ("mask", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("pair_gate", C.c_int32), ("mask_transition", C.c_int32), ("attention_first", C.c_int32),
     ]
 
 

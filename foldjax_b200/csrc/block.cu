@@ -61,6 +61,26 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
   if (i < total) out[i] = a[i] + b[i];
 }
 
+// dst[pair][:] = mask[pair] != 0 ? src[pair][:] : 0 for 128-channel bf16 pairs, one thread per
+// 16-byte chunk. With src == dst only the dropped pairs are written. The pair gate of
+// Protenix's block: z * pair_valid (protenix/models/trunk_blocks/pairformer.py:71-100).
+__global__ void gate_pairs_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const float* __restrict__ mask,
+                                  long long pairs) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= pairs * 16) return;
+  const bool keep = mask[idx >> 4] != 0.f;
+  if (!keep)
+    dst[idx] = make_uint4(0u, 0u, 0u, 0u);
+  else if (src != dst)
+    dst[idx] = src[idx];
+}
+
+// s[row][:] = 0 where mask[row] == 0 (the single-track gate of the same block)
+__global__ void gate_rows_kernel(float* __restrict__ s, const float* __restrict__ mask, int rows, int c) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx < static_cast<long long>(rows) * c && mask[idx / c] == 0.f) s[idx] = 0.f;
+}
+
 __global__ void fill_kernel(float* __restrict__ p, long long total, float v) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < total) p[i] = v;
@@ -201,58 +221,86 @@ extern "C" int b200tri_pairformer_forward(const b200tri_pairformer_args* a, b200
 
   const void* z_cur = a->z_in;
   const float* s_cur = a->s_in;
+  const long long pairs = static_cast<long long>(n) * n;
+  const bool gate = a->pair_gate != 0 && a->pair_mask != nullptr;
+  auto gate_pairs = [&](const void* src, void* dst) -> int {
+    count_launch();
+    gate_pairs_kernel<<<static_cast<unsigned>((pairs * 16 + 255) / 256), 256, 0, stream>>>(
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), a->pair_mask, pairs);
+    B200_CUDA_OK(cudaGetLastError());
+    return B200TRI_OK;
+  };
+  auto gate_rows = [&](float* sv) -> int {
+    count_launch();
+    gate_rows_kernel<<<static_cast<unsigned>((act + 255) / 256), 256, 0, stream>>>(sv, token_mask, n, c_s);
+    B200_CUDA_OK(cudaGetLastError());
+    return B200TRI_OK;
+  };
   for (int layer = 0; layer < a->n_blocks; ++layer) {
     const b200tri_pairformer_block_params P =
         a->stacked ? unstack(first, layer, c_s, a->heads_s) : a->params[layer];
     int rc;
-    // ---- pair track: z_cur -> w -> z_out -> w -> z_out, residual adds fused
-    for (int op = 0; op < 2; ++op) {
-      const b200tri_trimul_params& m = op == 0 ? P.tri_mul_out : P.tri_mul_in;
-      b200tri_trimul_args t = {};
-      t.n = n;
-      t.incoming = op;
-      t.eps = a->eps;
-      t.x = op == 0 ? z_cur : w;
-      t.mask = a->pair_mask;
-      t.norm_in_scale = m.norm_in_scale;
-      t.norm_in_bias = m.norm_in_bias;
-      t.p_in = m.p_in;
-      t.g_in = m.g_in;
-      t.norm_out_scale = m.norm_out_scale;
-      t.norm_out_bias = m.norm_out_bias;
-      t.p_out = m.p_out;
-      t.g_out = m.g_out;
-      t.residual = t.x;
-      t.out = op == 0 ? w : a->z_out;
-      t.workspace = ws + pl.sub;
-      t.workspace_bytes = pl.sub_bytes;
-      if ((rc = b200tri_trimul_forward(&t, stream_))) return rc;
+    // ---- pair track: the four triangle updates ping-pong between z_out and w (the first one
+    // reads the caller's z_in), residual adds fused; with the pair gate, dropped pairs are
+    // zeroed before the first update and after every update
+    if (gate && layer == 0) {
+      if ((rc = gate_pairs(z_cur, a->z_out))) return rc;  // a gated copy, or in place when they alias
+      z_cur = a->z_out;
     }
-    for (int op = 0; op < 2; ++op) {
-      const b200tri_triatt_params& m = op == 0 ? P.tri_att_start : P.tri_att_end;
-      b200tri_triatt_args t = {};
-      t.n = n;
-      t.starting = op == 0;
-      t.heads = 4;
-      t.head_dim = 32;
-      t.inf = a->tri_inf;
-      t.eps = a->eps;
-      t.x = op == 0 ? static_cast<const void*>(a->z_out) : w;
-      t.mask = a->pair_mask;
-      t.norm_scale = m.norm_scale;
-      t.norm_bias = m.norm_bias;
-      t.w_bias = m.w_bias;
-      t.w_q = m.w_q;
-      t.w_k = m.w_k;
-      t.w_v = m.w_v;
-      t.w_g = m.w_g;
-      t.w_o = m.w_o;
-      t.residual = t.x;
-      t.out = op == 0 ? w : a->z_out;
-      t.workspace = ws + pl.sub;
-      t.workspace_bytes = pl.sub_bytes;
-      if ((rc = b200tri_triatt_forward(&t, stream_))) return rc;
+    for (int k = 0; k < 4; ++k) {
+      // Boltz-2 / Protenix / OpenFold3 default: multiplications first; attention_first swaps the halves
+      const int op = a->attention_first ? (k + 2) % 4 : k;  // 0 out, 1 in, 2 start, 3 end
+      void* dst = z_cur == w ? a->z_out : w;
+      if (op < 2) {
+        const b200tri_trimul_params& m = op == 0 ? P.tri_mul_out : P.tri_mul_in;
+        b200tri_trimul_args t = {};
+        t.n = n;
+        t.incoming = op;
+        t.eps = a->eps;
+        t.x = z_cur;
+        t.mask = a->pair_mask;
+        t.norm_in_scale = m.norm_in_scale;
+        t.norm_in_bias = m.norm_in_bias;
+        t.p_in = m.p_in;
+        t.g_in = m.g_in;
+        t.norm_out_scale = m.norm_out_scale;
+        t.norm_out_bias = m.norm_out_bias;
+        t.p_out = m.p_out;
+        t.g_out = m.g_out;
+        t.residual = t.x;
+        t.out = dst;
+        t.workspace = ws + pl.sub;
+        t.workspace_bytes = pl.sub_bytes;
+        if ((rc = b200tri_trimul_forward(&t, stream_))) return rc;
+      } else {
+        const b200tri_triatt_params& m = op == 2 ? P.tri_att_start : P.tri_att_end;
+        b200tri_triatt_args t = {};
+        t.n = n;
+        t.starting = op == 2;
+        t.heads = 4;
+        t.head_dim = 32;
+        t.inf = a->tri_inf;
+        t.eps = a->eps;
+        t.x = z_cur;
+        t.mask = a->pair_mask;
+        t.norm_scale = m.norm_scale;
+        t.norm_bias = m.norm_bias;
+        t.w_bias = m.w_bias;
+        t.w_q = m.w_q;
+        t.w_k = m.w_k;
+        t.w_v = m.w_v;
+        t.w_g = m.w_g;
+        t.w_o = m.w_o;
+        t.residual = t.x;
+        t.out = dst;
+        t.workspace = ws + pl.sub;
+        t.workspace_bytes = pl.sub_bytes;
+        if ((rc = b200tri_triatt_forward(&t, stream_))) return rc;
+      }
+      if (gate && (rc = gate_pairs(dst, dst))) return rc;
+      z_cur = dst;
     }
+    // four updates from z_in (or z_out) end in z_out
     {
       b200tri_pair_transition_args t = {};
       t.rows = static_cast<int64_t>(n) * n;
@@ -269,7 +317,9 @@ extern "C" int b200tri_pairformer_forward(const b200tri_pairformer_args* a, b200
       t.out = a->z_out;  // row-local: in place
       t.workspace = ws + pl.sub;
       t.workspace_bytes = pl.sub_bytes;
+      t.row_mask = a->mask_transition ? a->pair_mask : nullptr;
       if ((rc = b200tri_pair_transition(&t, stream_))) return rc;
+      if (gate && (rc = gate_pairs(a->z_out, a->z_out))) return rc;
     }
     z_cur = a->z_out;
     if (!single) continue;
@@ -312,6 +362,7 @@ extern "C" int b200tri_pairformer_forward(const b200tri_pairformer_args* a, b200
     count_launch();
     add_kernel<<<static_cast<unsigned>((act + 255) / 256), 256, 0, stream>>>(s_cur, upd, act, a->s_out);
     B200_CUDA_OK(cudaGetLastError());
+    if (gate && (rc = gate_rows(a->s_out))) return rc;
     // transition_s: LN -> fc1 | fc2 -> silu(fc1) * fc2 -> fc3, added to s (transition.py:99-112)
     const int hid = P.transition_s.hidden;
     count_launch(2);
@@ -326,6 +377,7 @@ extern "C" int b200tri_pairformer_forward(const b200tri_pairformer_args* a, b200
     B200_CUDA_OK(cudaGetLastError());
     if ((rc = launch_linear_f32(hs, nullptr, P.transition_s.fc3, nullptr, n, hid, c_s, 0, a->s_out, a->s_out, stream)))
       return rc;
+    if (gate && (rc = gate_rows(a->s_out))) return rc;
     s_cur = a->s_out;
   }
   return B200TRI_OK;

@@ -63,6 +63,7 @@ struct Params {
   int nchunks;         // hidden / 64
   const uint32_t* ln;  // gamma, beta: 2 x 64 words
   const __nv_bfloat16* residual;
+  const float* row_mask;
   __nv_bfloat16* out;
   float eps;
   int* status;
@@ -235,6 +236,9 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       tc_fence_after();
       const long long r = (blockIdx.x + jt * static_cast<long long>(gridDim.x)) * 128 + row;
       const long long off = r * 128;
+      // optional per-row mask on the update (before the residual add), rounded to the trunk dtype
+      const float mkf = (p.row_mask && r < p.rows) ? p.row_mask[r] : 1.0f;
+      const uint32_t mk2 = pack_bf16x2(mkf, mkf);
 #pragma unroll 1
       for (int chunk = 0; chunk < 4; ++chunk) {
         uint32_t v[32];
@@ -249,6 +253,10 @@ pair_transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               u[e] = pack_bf16x2(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
+            if (p.row_mask) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) u[e] = bf16x2_mul(u[e], mk2);
+            }
             if (res) {
               const uint4 rv = res[q];
               u[0] = bf16x2_add(rv.x, u[0]);
@@ -402,6 +410,7 @@ extern "C" int b200tri_pair_transition(const b200tri_pair_transition_args* a, b2
   p.nchunks = a->hidden / HC;
   p.ln = ln;
   p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+  p.row_mask = a->row_mask;
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.eps = a->eps;
   p.status = status;

@@ -28,16 +28,21 @@ constexpr int MAX_HEADS = 16;
 constexpr int HD = 24;  // head width the token-attention kernel is built for
 
 // ---------------------------------------------------------------- pair bias
-// One thread per pair. With gamma folded into the projection,
+// One thread per pair, 128 pairs per tile. With gamma folded into the projection,
 //   bias_h = rstd * (sum_c x_c W'[c][h] - mean * sum_c W'[c][h]) + sum_c beta_c W[c][h],
-// so the normalised row is never formed: one pass for the statistics (two-pass
-// variance, as the reference computes it), one pass of heads FMAs per channel.
-__global__ void __launch_bounds__(128)
+// so the normalised row is never formed: one pass for the mean, one for the variance
+// (two-pass, as the reference computes it), one pass of heads FMAs per channel. The tile is
+// loaded with coalesced 16-byte loads into shared memory (16-byte chunks XOR-swizzled by the
+// pair index, so that neither the row-major stores nor the thread-per-row reads conflict)
+// and every pass reads it from there: the row never has to live in registers, and the
+// projection runs two heads per instruction (fma.f32x2).
+__global__ void __launch_bounds__(128, 4)
 pair_bias_kernel(const __nv_bfloat16* __restrict__ z, long long n_pairs, int n, int ld, int heads,
                  const __nv_bfloat16* __restrict__ ln_scale, const __nv_bfloat16* __restrict__ ln_bias,
                  const __nv_bfloat16* __restrict__ wz, float eps, float* __restrict__ bias) {
   __shared__ __align__(16) float w[C_Z][MAX_HEADS];  // gamma_c * Wz[c][h]
   __shared__ float sw[MAX_HEADS], bw[MAX_HEADS];
+  __shared__ __align__(16) uint4 tile_s[128 * 16];   // 128 pairs x 16 chunks of 8 channels
   for (int idx = threadIdx.x; idx < C_Z * MAX_HEADS; idx += blockDim.x) {
     const int c = idx / MAX_HEADS, h = idx % MAX_HEADS;
     w[c][h] = h < heads ? __bfloat162float(ln_scale[c]) * __bfloat162float(wz[c * heads + h]) : 0.f;
@@ -55,52 +60,73 @@ pair_bias_kernel(const __nv_bfloat16* __restrict__ z, long long n_pairs, int n, 
   }
   __syncthreads();
   const long long tiles = (n_pairs + 127) / 128;
+  const int p = threadIdx.x, key = p & 15;
   for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const long long pair = tile * 128 + threadIdx.x;
-    if (pair >= n_pairs) continue;
-    const uint4* src = reinterpret_cast<const uint4*>(z + pair * C_Z);
-    uint32_t x[64];
-#pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const uint4 v = src[q];
-      x[4 * q] = v.x;
-      x[4 * q + 1] = v.y;
-      x[4 * q + 2] = v.z;
-      x[4 * q + 3] = v.w;
+    const long long base = tile * 128;
+    const long long left = n_pairs - base;  // pairs of this tile that exist (>= 1)
+    const uint4* src = reinterpret_cast<const uint4*>(z + base * C_Z);
+#pragma unroll 8
+    for (int it = 0; it < 16; ++it) {
+      const int idx = it * 128 + p;  // chunk idx of the tile: pair idx / 16, chunk idx % 16
+      const int pr = idx >> 4, ch = idx & 15;
+      const uint4 v = pr < left ? src[idx] : make_uint4(0u, 0u, 0u, 0u);
+      tile_s[pr * 16 + (ch ^ (pr & 15))] = v;
     }
+    __syncthreads();
+    const uint4* row = tile_s + p * 16;
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int q = 0; q < 64; ++q) s4[q & 3] += bf16_lo(x[q]) + bf16_hi(x[q]);
+    for (int c = 0; c < 16; ++c) {
+      const uint4 v = row[c ^ key];
+      const uint32_t x4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s4[e] += bf16_lo(x4[e]) + bf16_hi(x4[e]);
+    }
     const float mean = ((s4[0] + s4[1]) + (s4[2] + s4[3])) * (1.0f / C_Z);
     float q4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int q = 0; q < 64; ++q) {
-      const float a = bf16_lo(x[q]) - mean, b = bf16_hi(x[q]) - mean;
-      q4[q & 3] = fmaf(a, a, q4[q & 3]);
-      q4[q & 3] = fmaf(b, b, q4[q & 3]);
-    }
-    const float rstd = rsqrtf(((q4[0] + q4[1]) + (q4[2] + q4[3])) * (1.0f / C_Z) + eps);
-    float acc[MAX_HEADS];
+    for (int c = 0; c < 16; ++c) {
+      const uint4 v = row[c ^ key];
+      const uint32_t x4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int h = 0; h < MAX_HEADS; ++h) acc[h] = 0.f;
-#pragma unroll 8
-    for (int q = 0; q < 64; ++q) {
-      const float a = bf16_lo(x[q]), b = bf16_hi(x[q]);
-      const float4* wa = reinterpret_cast<const float4*>(w[2 * q]);
-      const float4* wb = reinterpret_cast<const float4*>(w[2 * q + 1]);
-#pragma unroll
-      for (int h4 = 0; h4 < MAX_HEADS / 4; ++h4) {
-        const float4 fa = wa[h4], fb = wb[h4];
-        acc[4 * h4 + 0] = fmaf(b, fb.x, fmaf(a, fa.x, acc[4 * h4 + 0]));
-        acc[4 * h4 + 1] = fmaf(b, fb.y, fmaf(a, fa.y, acc[4 * h4 + 1]));
-        acc[4 * h4 + 2] = fmaf(b, fb.z, fmaf(a, fa.z, acc[4 * h4 + 2]));
-        acc[4 * h4 + 3] = fmaf(b, fb.w, fmaf(a, fa.w, acc[4 * h4 + 3]));
+      for (int e = 0; e < 4; ++e) {
+        const float a = bf16_lo(x4[e]) - mean, b = bf16_hi(x4[e]) - mean;
+        q4[e] = fmaf(a, a, q4[e]);
+        q4[e] = fmaf(b, b, q4[e]);
       }
     }
-    const long long i = pair / n, j = pair % n;
+    const float rstd = rsqrtf(((q4[0] + q4[1]) + (q4[2] + q4[3])) * (1.0f / C_Z) + eps);
+    float2 acc[MAX_HEADS / 2];
 #pragma unroll
-    for (int h = 0; h < MAX_HEADS; ++h)
-      if (h < heads) bias[(static_cast<long long>(h) * n + i) * ld + j] = rstd * (acc[h] - mean * sw[h]) + bw[h];
+    for (int h = 0; h < MAX_HEADS / 2; ++h) acc[h] = make_float2(0.f, 0.f);
+#pragma unroll 2
+    for (int c = 0; c < 16; ++c) {
+      const uint4 v = row[c ^ key];
+      const uint32_t x4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ch = 8 * c + 2 * e;  // channels ch (low half) and ch + 1 (high half)
+        const float a = bf16_lo(x4[e]), b = bf16_hi(x4[e]);
+        const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+        const float4* wa = reinterpret_cast<const float4*>(w[ch]);
+        const float4* wb = reinterpret_cast<const float4*>(w[ch + 1]);
+#pragma unroll
+        for (int h4 = 0; h4 < MAX_HEADS / 4; ++h4) {
+          const float4 fa = wa[h4], fb = wb[h4];
+          acc[2 * h4 + 0] = __ffma2_rn(b2, make_float2(fb.x, fb.y), __ffma2_rn(a2, make_float2(fa.x, fa.y), acc[2 * h4 + 0]));
+          acc[2 * h4 + 1] = __ffma2_rn(b2, make_float2(fb.z, fb.w), __ffma2_rn(a2, make_float2(fa.z, fa.w), acc[2 * h4 + 1]));
+        }
+      }
+    }
+    const long long pair = base + p;
+    if (pair < n_pairs) {
+      const long long i = pair / n, j = pair % n;
+#pragma unroll
+      for (int h = 0; h < MAX_HEADS; ++h)
+        if (h < heads)
+          bias[(static_cast<long long>(h) * n + i) * ld + j] = rstd * ((h & 1 ? acc[h >> 1].y : acc[h >> 1].x) - mean * sw[h]) + bw[h];
+    }
+    __syncthreads();  // the tile is overwritten by the next round's loads
   }
 }
 

@@ -78,6 +78,14 @@ class _Packed:
             self.heads_s = int(np.shape(_get(params["attention"], ("proj_z", "kernel")))[-1])
 
 
+#: what distinguishes the block of each model family at the level of this driver
+VARIANTS = {
+    "boltz2": {"pair_gate": False, "mask_transition": False},
+    "protenix": {"pair_gate": True, "mask_transition": False},
+    "openfold3": {"pair_gate": False, "mask_transition": True},
+}
+
+
 def pairformer_forward(
     params: Mapping[str, Any] | Sequence[Mapping[str, Any]],
     s: Any | None,
@@ -89,6 +97,10 @@ def pairformer_forward(
     num_blocks: int | None = None,
     tri_inf: float = 1e9,
     att_inf: float = 1e6,
+    variant: str = "boltz2",
+    pair_gate: bool | None = None,
+    mask_transition: bool | None = None,
+    attention_first: bool = False,
 ):
     """Run a stack of Pairformer blocks in one library call and return ``(s, z)``.
 
@@ -96,7 +108,20 @@ def pairformer_forward(
     ``[num_blocks, ...]`` (pass ``num_blocks``). ``s`` ``[B, N, c_s]`` float32 or None (pair
     track only), ``z`` ``[B, N, N, 128]`` bf16, ``mask`` ``[B, N]``, ``pair_mask`` ``[B, N, N]``.
     Device tensors in -> device tensors out (the inputs are not modified); host arrays in ->
-    copied to the GPU and back."""
+    copied to the GPU and back.
+
+    ``variant`` picks the block order of a model family: "boltz2" (default), "protenix" (the
+    pair tensor is multiplied by the pair mask before the first update and after every update,
+    the single track by the token mask, which defaults to the pair mask's diagonal:
+    protenix/models/trunk_blocks/pairformer.py:71-180) or "openfold3" (the pair transition's
+    update is multiplied by the pair mask: openfold3/models/pair_block.py:174-183).
+    ``pair_gate`` / ``mask_transition`` override the variant's choice; ``attention_first`` runs
+    the attention updates before the multiplications (OpenFold3's ``tri_mul_first=False``).
+    The arithmetic inside the ops is the Boltz-2 one either way (rounding points, layer norm)."""
+    if variant not in VARIANTS:
+        raise ValueError(f"Unsupported pairformer variant: {variant!r} (expected one of {sorted(VARIANTS)})")
+    gate = VARIANTS[variant]["pair_gate"] if pair_gate is None else bool(pair_gate)
+    mask_trans = VARIANTS[variant]["mask_transition"] if mask_transition is None else bool(mask_transition)
     dev.require_cuda()
     lib = _lib.load()
     host_in = dev.is_host_array(z)
@@ -127,6 +152,8 @@ def pairformer_forward(
         md = md.unsqueeze(0) if md.dim() == 1 else md
         if tuple(md.shape) != (b, n):
             raise ValueError(f"mask shape {tuple(md.shape)} does not match the pair tensor {tuple(zd.shape)}")
+    if gate and md is None and pmd is not None and single:
+        md = torch.diagonal(pmd, dim1=-2, dim2=-1).contiguous()  # single_valid = diag(pair_valid)
     if isinstance(params, Mapping):
         stacked, blocks = 1, int(num_blocks or 1)
         packed = [_Packed(params, single)]
@@ -152,7 +179,8 @@ def pairformer_forward(
             att_inf=float(att_inf), params=structs, z_in=zd[bi].data_ptr(), z_out=z_out[bi].data_ptr(),
             s_in=sd[bi].data_ptr() if single else None, s_out=s_out[bi].data_ptr() if single else None,
             pair_mask=pmd[bi].data_ptr() if pmd is not None else None, mask=md[bi].data_ptr() if md is not None else None,
-            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes)
+            workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+            pair_gate=int(gate), mask_transition=int(mask_trans), attention_first=int(bool(attention_first)))
         _lib.check(lib.b200tri_pairformer_forward(C.byref(args), C.c_void_p(dev.stream_ptr())))
     if squeeze:
         z_out = z_out[0]

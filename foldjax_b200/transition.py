@@ -31,6 +31,7 @@ def transition_forward(
     *,
     residual: Any | None = None,
     out: torch.Tensor | None = None,
+    mask: Any | None = None,
 ):
     """Boltz Transition block: ``(silu(LN(x) @ fc1) * (LN(x) @ fc2)) @ fc3``.
 
@@ -43,7 +44,10 @@ def transition_forward(
     intermediate; the fused kernel never materialises it, so both are validated
     and otherwise ignored, the way the reference ignores them for its fused GLU
     backend. ``residual`` (optional, may be ``x`` itself) fuses the caller's
-    ``z + update``; ``out`` may alias ``x`` only if it also is the residual.
+    ``z + update``; ``out`` may alias ``x`` only if it also is the residual. ``mask`` (optional,
+    one value per row, i.e. the shape of ``x`` without its channel axis) multiplies the update
+    before the residual add: OpenFold3's masked transition
+    (src/foldjax/models/openfold3/models/primitives.py:133-150).
     """
     if chunk_size is not None and chunk_size <= 0:
         raise ValueError(f"chunk_size must be positive, got {chunk_size}")
@@ -81,12 +85,17 @@ def transition_forward(
             f"{tuple(leaves['fc1'].shape)}, {tuple(leaves['fc2'].shape)}, {tuple(leaves['fc3'].shape)}")
     if rows == 0:
         return out
+    md = None
+    if mask is not None:
+        md = dev.to_device(mask, torch.float32)
+        if md.numel() != rows:
+            raise ValueError(f"mask shape {tuple(md.shape)} does not give one value per row of x {tuple(xd.shape)}")
     nbytes = lib.b200tri_pair_transition_workspace_bytes(hidden)
     ws = dev.workspace(nbytes, "pair_transition")
     args = _lib.PairTransitionArgs(
         rows=rows, channels=C_Z, hidden=hidden, eps=float(eps),
         x=xd.data_ptr(), residual=_ptr(rd), out=out.data_ptr(),
-        workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes,
+        workspace=dev.aligned_ptr(ws), workspace_bytes=nbytes, row_mask=_ptr(md),
         **{k: v.data_ptr() for k, v in leaves.items()},
     )
     _lib.check(lib.b200tri_pair_transition(C.byref(args), C.c_void_p(dev.stream_ptr())))

@@ -554,6 +554,11 @@ typedef struct {
   void* out;             /* bf16 [rows][128] */
   void* workspace;
   size_t workspace_bytes;
+  /* Optional float32 [rows]: the update of row r is multiplied by row_mask[r] (rounded to
+   * bf16) before the residual add - OpenFold3's masked transition, swiglu_transition(...,
+   * mask=pair_mask), src/foldjax/models/openfold3/models/primitives.py:133-150 as called by
+   * pair_block.py:174-183. NULL = no mask. */
+  const float* row_mask;
 } b200tri_pair_transition_args;
 
 size_t b200tri_pair_transition_workspace_bytes(int32_t hidden);
@@ -646,6 +651,18 @@ typedef struct {
   const float* mask;      /* [n] or NULL (= ones) */
   void* workspace;        /* b200tri_pairformer_workspace_bytes, 1 KiB aligned */
   size_t workspace_bytes;
+  /* Variants of the block in the other model families (all 0 = the Boltz-2 block):
+   * pair_gate: z is multiplied by (pair_mask != 0) before the first update and after every
+   *   update, and s by (mask != 0) after both single-track updates - Protenix's block,
+   *   src/foldjax/models/protenix/models/trunk_blocks/pairformer.py:71-180 (pass mask = the
+   *   diagonal of pair_mask, as it does).
+   * mask_transition: the pair transition's update is multiplied by pair_mask before it is
+   *   added - OpenFold3's _mask_trans default, openfold3/models/pair_block.py:174-183.
+   * attention_first: the two attention updates run before the two multiplications
+   *   (tri_mul_first = False of OpenFold3's template pair block, pair_block.py:151-171). */
+  int32_t pair_gate;
+  int32_t mask_transition;
+  int32_t attention_first;
 } b200tri_pairformer_args;
 
 size_t b200tri_pairformer_workspace_bytes(int32_t n, int32_t c_s, int32_t heads_s, int32_t hidden_z, int32_t hidden_s);

@@ -449,18 +449,42 @@ def random_attention_pair_bias_params(rng: np.random.Generator, c_s: int = 384, 
 
 # ------------------------------------------------------------- one Pairformer block
 def pairformer_layer(params: Params, s: np.ndarray | None, z: np.ndarray, mask: np.ndarray | None,
-                     pair_mask: np.ndarray | None, eps: float = 1e-5, dtype: str = "float64"):
+                     pair_mask: np.ndarray | None, eps: float = 1e-5, dtype: str = "float64", *,
+                     pair_gate: bool = False, mask_transition: bool = False, attention_first: bool = False):
     """pairformer_layer_forward, trunk_blocks/pairformer.py:126-206: the four triangle updates
     and the pair transition on z (trunk dtype, residual sums rounded to it), then the single
     track in float32 (float64 here when ``dtype`` is "float64"): s += attention_pair_bias(LN(s),
-    z) ; s += transition_s(s). s = None runs the pair track only. Returns (s, z)."""
+    z) ; s += transition_s(s). s = None runs the pair track only. Returns (s, z).
+
+    Block variants of the other model families, on the same op arithmetic:
+    ``pair_gate`` - Protenix's block (protenix/models/trunk_blocks/pairformer.py:71-180): z is
+    multiplied by (pair_mask != 0) first and after every update, s by the token gate (the
+    diagonal of the pair mask unless ``mask`` is given) first and after both of its updates;
+    ``mask_transition`` - OpenFold3's pair block (openfold3/models/pair_block.py:174-183): the
+    pair transition's update is multiplied by the pair mask;
+    ``attention_first`` - its ``tri_mul_first=False`` order (pair_block.py:151-171)."""
     pr = _Prec(dtype)
     z = pr.arr(z)
-    z = pr.r(z + triangle_multiplication(params["tri_mul_out"], z, pair_mask, "outgoing", eps, dtype))
-    z = pr.r(z + triangle_multiplication(params["tri_mul_in"], z, pair_mask, "incoming", eps, dtype))
-    z = pr.r(z + triangle_attention(params["tri_att_start"], z, pair_mask, True, eps=eps, dtype=dtype))
-    z = pr.r(z + triangle_attention(params["tri_att_end"], z, pair_mask, False, eps=eps, dtype=dtype))
-    z = pr.r(z + transition(params["transition_z"], z, eps, dtype))
+    gate_z = None
+    if pair_gate and pair_mask is not None:
+        gate_z = (np.asarray(pair_mask) != 0).astype(z.dtype)[..., None]
+        z = z * gate_z
+        if mask is None:
+            mask = np.diagonal(np.asarray(pair_mask) != 0, axis1=-2, axis2=-1).astype(np.float32)
+
+    def gated(v):
+        return v if gate_z is None else v * gate_z
+
+    mults = (lambda v: triangle_multiplication(params["tri_mul_out"], v, pair_mask, "outgoing", eps, dtype),
+             lambda v: triangle_multiplication(params["tri_mul_in"], v, pair_mask, "incoming", eps, dtype))
+    atts = (lambda v: triangle_attention(params["tri_att_start"], v, pair_mask, True, eps=eps, dtype=dtype),
+            lambda v: triangle_attention(params["tri_att_end"], v, pair_mask, False, eps=eps, dtype=dtype))
+    for update in (atts + mults if attention_first else mults + atts):
+        z = gated(pr.r(z + update(z)))
+    upd = transition(params["transition_z"], z, eps, dtype)
+    if mask_transition and pair_mask is not None:
+        upd = pr.r(upd * pr.r(np.asarray(pair_mask, dtype=upd.dtype))[..., None])
+    z = gated(pr.r(z + upd))
     if s is None:
         return None, z
     wide = "float64" if dtype == "float64" else "float32"
@@ -468,9 +492,16 @@ def pairformer_layer(params: Params, s: np.ndarray | None, z: np.ndarray, mask: 
     s = np.asarray(s, dtype=work)
     if mask is None:
         mask = np.ones(s.shape[:2], dtype=work)
+    gate_s = (np.asarray(mask) != 0).astype(work)[..., None] if gate_z is not None else None
+    if gate_s is not None:
+        s = s * gate_s
     s_normed = layer_norm(s, params["pre_norm_s"]["scale"], params["pre_norm_s"]["bias"], eps, wide)
     s = s + attention_pair_bias(params["attention"], s_normed, z, mask, k_in=s_normed, eps=eps, dtype=wide)
+    if gate_s is not None:
+        s = s * gate_s
     s = s + transition(params["transition_s"], s, eps, wide)
+    if gate_s is not None:
+        s = s * gate_s
     return s, z
 
 

@@ -158,3 +158,32 @@ def test_sampled_triatt_elements_equal_the_full_restatement(starting, dtype):
     else:
         assert np.mean(got == ref) > 0.97
         np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-3)
+
+
+def test_block_variants_of_the_other_model_families():
+    """pair_gate (Protenix), mask_transition (OpenFold3) and attention_first on the block
+    restatement: the gate zeroes dropped pairs and gated tokens and, with a mask that is not an
+    outer product, changes kept pairs too (a dropped pair's bias no longer reaches the rows that
+    keep its key); the masked transition only changes dropped pairs; the order matters."""
+    rng = np.random.default_rng(0)
+    params = orc.random_pairformer_params(rng, c_s=48, heads_s=2, ln_noise=0.1)
+    n = 12
+    z = rng.standard_normal((1, n, n, 128)).astype(np.float32)
+    s = rng.standard_normal((1, n, 48)).astype(np.float32)
+    pair_mask = orc.pad_mask(n, 3).copy()
+    pair_mask[0, 1, 2] = 0.0
+    pair_mask[0, 4, 0] = 0.0
+    keep = pair_mask[0] == 1
+    s0, z0 = orc.pairformer_layer(params, s, z, None, pair_mask, dtype="float32")
+    s1, z1 = orc.pairformer_layer(params, s, z, None, pair_mask, dtype="float32", pair_gate=True)
+    assert np.all(z1[0][~keep] == 0.0) and np.all(s1[0][n - 3:] == 0.0)
+    assert np.abs(z1 - z0)[0][keep].max() > 1e-4
+    _, z2 = orc.pairformer_layer(params, s, z, None, pair_mask, dtype="float32", mask_transition=True)
+    assert np.abs(z2 - z0)[0][keep].max() == 0.0 and np.abs(z2 - z0)[0][~keep].max() > 1e-4
+    _, z3 = orc.pairformer_layer(params, s, z, None, pair_mask, dtype="float32", attention_first=True)
+    assert np.abs(z3 - z0).max() > 1e-4
+    # with an all-ones mask the gate and the masked transition are no-ops
+    ones = np.ones_like(pair_mask)
+    a = orc.pairformer_layer(params, s, z, None, ones, dtype="float32")
+    b = orc.pairformer_layer(params, s, z, None, ones, dtype="float32", pair_gate=True, mask_transition=True)
+    assert np.array_equal(a[1], b[1]) and np.array_equal(a[0], b[0])

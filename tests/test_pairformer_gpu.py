@@ -94,6 +94,42 @@ def test_pair_track_only_equals_the_per_op_block(cuda_device):
     assert torch.equal(z_one, triangle_block_forward(pd, zd, pmd))
 
 
+@pytest.mark.parametrize("variant,flags", [
+    ("protenix", dict(pair_gate=True)),
+    ("openfold3", dict(mask_transition=True)),
+    ("boltz2", dict(attention_first=True)),
+])
+def test_block_variants_match_the_oracle(cuda_device, variant, flags):
+    """The block orders of the other model families: Protenix's pair gate (with a mask that is
+    NOT an outer product, so the gate before the first update matters), OpenFold3's masked
+    transition, and attention before multiplication."""
+    from foldjax_b200 import _lib
+    from foldjax_b200.pairformer import pairformer_forward
+
+    params, s, z, mask, pair_mask = _case(21, 72, 7)
+    pair_mask = pair_mask.copy()
+    rng = np.random.default_rng(5)
+    drop = rng.random(pair_mask.shape) < 0.05
+    drop[0, np.arange(72), np.arange(72)] = False  # the diagonal (the token gate) stays as padded
+    pair_mask[drop] = 0.0
+    kw = dict(attention_first=True) if "attention_first" in flags else {}
+    s_got, z_got = pairformer_forward([params], s, z, mask, pair_mask, variant=variant, **kw)
+    _lib.device_status()
+    s_ref, z_ref = orc.pairformer_layer(params, s, z, mask, pair_mask, dtype="bfloat16", **flags)
+    rows_ok = pair_mask[0].any(axis=1)
+    valid = (rows_ok[:, None] & pair_mask[0].any(axis=0)[None, :])[None, :, :, None]
+    print(assert_parity(z_ref, z_got, where=np.broadcast_to(valid, z_ref.shape), label=f"block z, {variant} {flags}"))
+    tok = mask[0].astype(bool)
+    err = orc.error_vs(s_ref[0][tok], s_got[0][tok])
+    print(f"block s, {variant}: {err}")
+    assert err["mean_abs_over_rms"] < 2e-3 and err["max_abs_over_rms"] < 2e-2, err
+    if variant == "protenix":
+        assert np.all(z_got[0][pair_mask[0] == 0] == 0.0) and np.all(s_got[0][~tok] == 0.0)
+    # the variant does change the result
+    _, z_plain = pairformer_forward([params], s, z, mask, pair_mask)
+    assert not np.array_equal(z_plain, z_got)
+
+
 def test_streamed_host_blocks_equal_one_call_each(cuda_device):
     """stream_host_blocks (copies of neighbouring items overlapped with the kernels) gives, item
     by item, exactly what triangle_block_forward gives for that item alone; five different

@@ -100,6 +100,26 @@ def test_large_case_properties(cuda_device):
     assert_parity(ref, part.float().cpu().numpy(), label="rows 100..102 of 512x512")
 
 
+def test_masked_update(cuda_device):
+    """mask= multiplies the update row by row before the residual add (OpenFold3's masked
+    transition): dropped rows come back as the residual, kept rows as without a mask - bit for
+    bit, since a 0/1 mask multiplies exactly."""
+    from foldjax_b200.transition import transition_forward
+
+    params, x = _case(17, (9, 150))
+    rng = np.random.default_rng(3)
+    mask = (rng.random((9, 150)) > 0.3).astype(np.float32)
+    plain = transition_forward(params, x, residual=x)
+    masked = transition_forward(params, x, residual=x, mask=mask)
+    keep = mask.astype(bool)
+    assert np.array_equal(masked[keep], plain[keep])
+    assert np.array_equal(masked[~keep], x[~keep])
+    update_only = transition_forward(params, x, mask=mask)
+    assert np.all(update_only[~keep] == 0.0) and np.array_equal(update_only[keep], transition_forward(params, x)[keep])
+    with pytest.raises(ValueError, match="one value per row"):
+        transition_forward(params, x, mask=mask[:, :100])
+
+
 def test_rejects_bad_arguments(cuda_device):
     from foldjax_b200 import _device as dev, _lib
     from foldjax_b200.transition import transition_forward
