@@ -816,8 +816,20 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   if (cm->world > 1 && pl.rpb == 64)
     for (k_split = m >= 4 ? 1 : 4 / m; k_split > 1 && (n_c % k_split || (n_c / k_split) % 128); k_split /= 2) {
     }
+  // Which operand travels whole in the first group: the one the busiest rank sends less of. On a
+  // square grid an outgoing rank sends one `a` tile but up to two `b` tiles, so there `a` goes
+  // first and `b` is chunked: the chunks are then output COLUMNS (rows of `b`), a multiple of the
+  // contraction's 256-column tile wide. Everywhere else (`a` panels are the larger ones) the
+  // chunks are output rows, as described above.
+  bool by_cols = false;
+  if (!incoming && m == 1 && cm->world > 1 && pl.rpb == 64)
+    for (int k = 4; k >= 2 && !by_cols; --k)
+      if (n_c % k == 0 && (n_c / k) % 256 == 0) {
+        by_cols = true;
+        k_split = k;
+      }
   const int G = m * k_split;
-  const int64_t h = n_c / k_split;  // rows per chunk
+  const int64_t h = n_c / k_split;  // rows (or columns) per chunk
   const size_t rb_bytes = static_cast<size_t>(128) * 64 * pl.ld * 2;
   auto chunk_off = [&](int q) { return k_split > 1 ? static_cast<size_t>(q * h / 64) * rb_bytes : 0; };
   const size_t chunk_bytes = k_split > 1 ? static_cast<size_t>(h / 64) * rb_bytes : blk_bytes;
@@ -829,15 +841,23 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     const int s = g / k_split, q = g % k_split;  // n_c-row block and chunk inside it
     rc = post_exchange(
         cm, ws, pull, msgs,
-        [&](const Msg& msg) { return msg.what == WHAT_B ? g == 0 : (!incoming || msg.slot0 == s); },
+        [&](const Msg& msg) {
+          if (by_cols) return msg.what == WHAT_A ? g == 0 : true;
+          return msg.what == WHAT_B ? g == 0 : (!incoming || msg.slot0 == s);
+        },
         [&](const Msg& msg, bool send, int who, std::vector<Piece>& out) {
           if (msg.what == WHAT_B) {
+            const size_t off = by_cols ? chunk_off(g) : 0, bytes = by_cols ? chunk_bytes : blk_bytes;
             if (send) {
               const size_t b_loc = incoming ? pl.b_all + blk_bytes * (who / cm->cols) : pl.b_loc;
-              out.push_back({b_loc + (msg.block < 0 ? 0 : blk_bytes * msg.block), blk_bytes});
+              out.push_back({b_loc + (msg.block < 0 ? 0 : blk_bytes * msg.block) + off, bytes});
             } else {
-              out.push_back({pl.b_all + blk_bytes * msg.slot0, blk_bytes});
+              out.push_back({pl.b_all + blk_bytes * msg.slot0 + off, bytes});
             }
+            return;
+          }
+          if (by_cols) {  // the whole tile (m = 1: one block)
+            out.push_back({pl.a_all + blk_bytes * (send ? who % cm->cols : msg.slot0), blk_bytes});
             return;
           }
           // `a`: the sender's local array has the receiver slot's layout; outgoing messages span
@@ -849,7 +869,7 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
             base = send ? pl.a_loc : pl.a_all + blk_bytes * (static_cast<size_t>(msg.slot0) * cm->rows + msg.slot1);
           out.push_back({base + chunk_off(q), chunk_bytes});
         },
-        stream, g == 0 && chunk_bytes < blk_bytes ? WHAT_B : -1);
+        stream, g == 0 && chunk_bytes < blk_bytes ? (by_cols ? WHAT_A : WHAT_B) : -1);
     if (rc) return rc;
     B200_CUDA_OK(cudaEventRecord(g + 1 < G ? cm->ev_part[g] : cm->ev_rest, cm->stream));
   }
@@ -862,22 +882,26 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     const bool last = g + 1 == G;
     B200_CUDA_OK(cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
     b200tri_trimul_contract_args ca = {};
-    ca.n_i = static_cast<int32_t>(h);
-    ca.n_j = static_cast<int32_t>(n_c);
+    ca.n_i = static_cast<int32_t>(by_cols ? n_r : h);
+    ca.n_j = static_cast<int32_t>(by_cols ? h : n_c);
     ca.n_k = pl.n_k;
     ca.n_src = pl.n_src;
-    if (!incoming) {
+    if (by_cols) {
+      ca.a = ws + pl.a_all;
+      ca.a_src_stride = static_cast<int64_t>(pl.blk);
+    } else if (!incoming) {
       ca.a = ws + pl.a_all + blk_bytes * s + chunk_off(q);
       ca.a_src_stride = static_cast<int64_t>(pl.blk) * m;
     } else {
       ca.a = ws + pl.a_all + blk_bytes * (static_cast<size_t>(s) * cm->rows) + chunk_off(q);
       ca.a_src_stride = static_cast<int64_t>(pl.blk);
     }
-    ca.b = ws + pl.b_all;
+    ca.b = ws + pl.b_all + (by_cols ? chunk_off(g) : 0);
     ca.b_src_stride = static_cast<int64_t>(pl.blk);
     ca.a_ld = ca.b_ld = pl.ld;
     ca.a_chan_stride = ca.b_chan_stride = static_cast<int64_t>(pl.rpb) * pl.ld;
-    ca.out_bf16 = ws + pl.t + static_cast<size_t>(2) * (static_cast<size_t>(s) * n_c + static_cast<size_t>(q) * h) * t_row;
+    ca.out_bf16 = by_cols ? ws + pl.t + static_cast<size_t>(2) * g * h
+                          : ws + pl.t + static_cast<size_t>(2) * (static_cast<size_t>(s) * n_c + static_cast<size_t>(q) * h) * t_row;
     ca.out_ld = pl.ldt;
     ca.out_chan_stride = t_chan;
     ca.a_rows_per_block = ca.b_rows_per_block = pl.rpb;
@@ -888,18 +912,20 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     b200::SmReserve room(last ? 0 : cm->sm_reserve);
     if ((rc = b200tri_trimul_contract(&ca, stream_))) return rc;
 
-    // output stage of the same rows (row-local)
-    const int64_t row0 = static_cast<int64_t>(s) * n_c + static_cast<int64_t>(q) * h;
+    // output stage of the same rows (or columns): it is local to a pair
+    const int64_t row0 = by_cols ? 0 : static_cast<int64_t>(s) * n_c + static_cast<int64_t>(q) * h;
+    const int64_t col0 = by_cols ? static_cast<int64_t>(g) * h : 0;
+    const size_t pair0 = static_cast<size_t>(2) * (row0 * n_c + col0) * 128;  // byte offset of pair (row0, col0) in the tile
     b200tri_trimul_finish_args fa = {};
-    fa.n_i = static_cast<int32_t>(h);
-    fa.n_j = static_cast<int32_t>(n_c);
+    fa.n_i = static_cast<int32_t>(by_cols ? n_r : h);
+    fa.n_j = static_cast<int32_t>(by_cols ? h : n_c);
     fa.eps = a->eps;
-    fa.t = ws + pl.t + static_cast<size_t>(2) * row0 * t_row;
+    fa.t = ws + pl.t + static_cast<size_t>(2) * (row0 * t_row + col0);
     fa.t_ld = pl.ldt;
     fa.t_chan_stride = t_chan;
     fa.t_rows_per_block = pl.t_rpb;
     fa.t_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
-    fa.x = static_cast<const uint8_t*>(a->x) + static_cast<size_t>(2) * row0 * n_c * 128;
+    fa.x = static_cast<const uint8_t*>(a->x) + pair0;
     fa.xs_i = n_c * 128;
     fa.xs_j = 128;
     fa.norm_in_scale = a->norm_in_scale;
@@ -908,8 +934,8 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     fa.norm_out_bias = a->norm_out_bias;
     fa.p_out = a->p_out;
     fa.g_out = a->g_out;
-    fa.residual = a->residual ? static_cast<const uint8_t*>(a->residual) + static_cast<size_t>(2) * row0 * n_c * 128 : nullptr;
-    fa.out = static_cast<uint8_t*>(a->out) + static_cast<size_t>(2) * row0 * n_c * 128;
+    fa.residual = a->residual ? static_cast<const uint8_t*>(a->residual) + pair0 : nullptr;
+    fa.out = static_cast<uint8_t*>(a->out) + pair0;
     fa.os_i = n_c * 128;
     fa.os_j = 128;
     fa.workspace = ws + pl.fin;

@@ -28,8 +28,8 @@ def _run(world: int, tokens: int, transport: str = "push", layout: str = "") -> 
     return done.stdout
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (2, 256), (4, 512), (4, 256), (8, 1024), (8, 256),
-                                          (8, 3072)])
+@pytest.mark.parametrize("world,tokens", [(2, 512), (2, 200), (2, 256), (4, 512), (4, 256), (4, 1024), (4, 1536),
+                                          (8, 1024), (8, 256), (8, 3072)])
 def test_context_parallel_matches_single_gpu(world, tokens):
     """Tiles written into the peers' mapped workspaces by the senders (the default transport)."""
     out = _run(world, tokens)
