@@ -152,6 +152,12 @@ class AttentionPairBiasArgs(C.Structure):
     ]
 
 
+class CpEvent(C.Structure):
+    _fields_ = [(k, C.c_int32) for k in ("kind", "group", "round", "src", "dst", "what", "block", "slot0", "slot1",
+                                          "n_i", "n_j", "reserved")] + [
+        ("src_off", C.c_int64), ("dst_off", C.c_int64), ("bytes", C.c_int64), ("off", C.c_int64 * 4)]
+
+
 class CpMsg(C.Structure):
     _fields_ = [("src", C.c_int32), ("dst", C.c_int32), ("what", C.c_int32), ("block", C.c_int32),
                 ("slot0", C.c_int32), ("slot1", C.c_int32)]
@@ -238,6 +244,7 @@ STRUCTS = {
     "b200tri_pair_transition_args": PairTransitionArgs,
     "b200tri_attention_pair_bias_args": AttentionPairBiasArgs,
     "b200tri_cp_msg": CpMsg,
+    "b200tri_cp_event": CpEvent,
     "b200tri_trimul_cp_args": TrimulCpArgs,
     "b200tri_triatt_cp_args": TriattCpArgs,
     "b200tri_pairformer_args": PairformerArgs,
@@ -299,6 +306,9 @@ SIGNATURES = {
     "b200tri_comm_probe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200tri_cp_plan": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(CpMsg), C.c_int32]),
     "b200tri_cp_rounds": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32]),
+    "b200tri_cp_dry_run": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                     C.POINTER(CpEvent), C.c_int32]),
+    "b200tri_cp_layout": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64)]),
     "b200tri_trimul_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),
     "b200tri_trimul_cp": (C.c_int, [C.c_void_p, C.POINTER(TrimulCpArgs), C.c_void_p]),
     "b200tri_triatt_cp_workspace_bytes": (C.c_size_t, [C.c_void_p, C.c_int32]),

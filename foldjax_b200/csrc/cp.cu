@@ -47,6 +47,10 @@ struct b200tri_comm {
   bool push = true;
   int n_copy = 1;
   int sm_reserve = 4;  // SMs left free beside a kernel that runs while tokens travel
+  // Dry run (b200tri_cp_dry_run): no CUDA or NCCL call is made; the copies this rank would issue
+  // and the launches it would make are written to this log instead, for checks on a CPU.
+  std::vector<b200tri_cp_event>* dry = nullptr;
+  int dry_group = 0;
   cudaStream_t copy_stream[4] = {nullptr, nullptr, nullptr, nullptr};  // [0] is `stream`
   cudaEvent_t ev_fork = nullptr, ev_join[4] = {nullptr, nullptr, nullptr, nullptr};
 };
@@ -241,15 +245,52 @@ template <typename Want, typename Views>
 int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Msg>& msgs, Want want, Views views,
                   cudaStream_t compute, int wide_what = -1) {
   auto big = [&](const Msg& msg) { return msg.what == wide_what; };  // messages larger than the others
-  const Nccl* api = nccl_api();
-  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
   std::vector<Piece> send, recv;
-  // with timing on, the span of this exchange on the exchange stream (it starts when the stream
-  // has seen the caller's "tiles are ready" event, so it is transfer time plus peer skew)
-  TimedLaunch timed(K_CP_EXCHANGE, cm->stream);
   auto remote = [&](const Msg& msg) {
     return want(msg) && msg.src != msg.dst && (msg.src == cm->rank || msg.dst == cm->rank);
   };
+  if (cm->dry) {
+    // the copies this rank would issue, in issue order: local ones, then the remote ones it
+    // sends (push) or fetches (pull) round by round
+    const int group = cm->dry_group++;
+    const std::vector<int> round = copy_rounds(msgs, cm->world, want, big);
+    int n_rounds = 0;
+    for (int r : round) n_rounds = std::max(n_rounds, r + 1);
+    auto log = [&](const Msg& msg, int kind, int rnd) {
+      send.clear();
+      recv.clear();
+      views(msg, true, msg.src, send);
+      views(msg, false, msg.dst, recv);
+      for (size_t i = 0; i < send.size(); ++i) {
+        b200tri_cp_event e = {};
+        e.kind = kind;
+        e.group = group;
+        e.round = rnd;
+        e.src = msg.src;
+        e.dst = msg.dst;
+        e.what = msg.what;
+        e.block = msg.block;
+        e.slot0 = msg.slot0;
+        e.slot1 = msg.slot1;
+        e.src_off = static_cast<int64_t>(send[i].off);
+        e.dst_off = static_cast<int64_t>(recv[i].off);
+        e.bytes = static_cast<int64_t>(send[i].bytes);
+        cm->dry->push_back(e);
+      }
+    };
+    for (const Msg& msg : msgs)
+      if (want(msg) && msg.src == cm->rank && msg.dst == cm->rank) log(msg, B200TRI_CP_EVENT_LOCAL_COPY, -1);
+    for (int r = 0; r < n_rounds; ++r)
+      for (size_t i = 0; i < msgs.size(); ++i)
+        if (round[i] == r && (pull ? (cm->push ? msgs[i].src : msgs[i].dst) : msgs[i].src) == cm->rank)
+          log(msgs[i], B200TRI_CP_EVENT_COPY, r);
+    return B200TRI_OK;
+  }
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  // with timing on, the span of this exchange on the exchange stream (it starts when the stream
+  // has seen the caller's "tiles are ready" event, so it is transfer time plus peer skew)
+  TimedLaunch timed(K_CP_EXCHANGE, cm->stream);
   // local messages
   for (const Msg& msg : msgs) {
     if (!want(msg) || msg.src != cm->rank || msg.dst != cm->rank) continue;
@@ -352,7 +393,33 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
   return token_round(push);
 }
 
+// CUDA calls of the ops that a dry run skips
+#define CP_CUDA(cm, call)               \
+  do {                                  \
+    if (!(cm)->dry) B200_CUDA_OK(call); \
+  } while (0)
+
+// a launch the op would make, for the dry-run log: offsets are relative to the workspace
+// (off[0..2]) and to the rank's tile (off[3])
+void log_launch(b200tri_comm* cm, int kind, int group, int n_i, int n_j, int64_t o0, int64_t o1, int64_t o2, int64_t o3) {
+  if (!cm->dry) return;
+  b200tri_cp_event e = {};
+  e.kind = kind;
+  e.group = group;
+  e.round = -1;
+  e.src = e.dst = cm->rank;
+  e.what = e.block = e.slot0 = e.slot1 = -1;
+  e.n_i = n_i;
+  e.n_j = n_j;
+  e.off[0] = o0;
+  e.off[1] = o1;
+  e.off[2] = o2;
+  e.off[3] = o3;
+  cm->dry->push_back(e);
+}
+
 int check_comm(const b200tri_comm* cm, const char* who) {
+  if (cm != nullptr && cm->dry != nullptr) return B200TRI_OK;
   B200_REQUIRE(cm != nullptr && cm->nccl != nullptr, B200TRI_ERR_INVALID, "%s: null or destroyed communicator", who);
   int dev = -1;
   B200_CUDA_OK(cudaGetDevice(&dev));
@@ -804,7 +871,9 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   pa.rows_per_block = pl.rpb;
   pa.workspace = ws + pl.proj;
   pa.workspace_bytes = b200tri_trimul_project_workspace_bytes();
-  if ((rc = b200tri_trimul_project(&pa, stream_))) return rc;
+  log_launch(cm, B200TRI_CP_EVENT_PROJECT, -1, pa.n_outer, pa.n_inner, static_cast<uint8_t*>(pa.a) - ws,
+             static_cast<uint8_t*>(pa.b) - ws, 0, 0);
+  if (!cm->dry && (rc = b200tri_trimul_project(&pa, stream_))) return rc;
 
   // Exchange and contraction, in row chunks: the output rows of the tile are cut into G chunks
   // (k_split per n_c-row block); group g of the exchange carries chunk g of every `a` message
@@ -833,8 +902,8 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   const size_t rb_bytes = static_cast<size_t>(128) * 64 * pl.ld * 2;
   auto chunk_off = [&](int q) { return k_split > 1 ? static_cast<size_t>(q * h / 64) * rb_bytes : 0; };
   const size_t chunk_bytes = k_split > 1 ? static_cast<size_t>(h / 64) * rb_bytes : blk_bytes;
-  B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
-  B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  CP_CUDA(cm, cudaEventRecord(cm->ev_ready, stream));
+  CP_CUDA(cm, cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
   const std::vector<Msg> msgs =
       build_plan(Grid{cm->rows, cm->cols, m}, incoming ? B200TRI_CP_TRIMUL_INCOMING : B200TRI_CP_TRIMUL_OUTGOING);
   for (int g = 0; g < G; ++g) {
@@ -871,7 +940,7 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
         },
         stream, g == 0 && chunk_bytes < blk_bytes ? (by_cols ? WHAT_A : WHAT_B) : -1);
     if (rc) return rc;
-    B200_CUDA_OK(cudaEventRecord(g + 1 < G ? cm->ev_part[g] : cm->ev_rest, cm->stream));
+    CP_CUDA(cm, cudaEventRecord(g + 1 < G ? cm->ev_part[g] : cm->ev_rest, cm->stream));
   }
 
   // one contraction launch per output chunk walks all k-sources (fp32 accumulation on chip)
@@ -880,7 +949,7 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
   for (int g = 0; g < G; ++g) {
     const int s = g / k_split, q = g % k_split;
     const bool last = g + 1 == G;
-    B200_CUDA_OK(cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
+    CP_CUDA(cm, cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
     b200tri_trimul_contract_args ca = {};
     ca.n_i = static_cast<int32_t>(by_cols ? n_r : h);
     ca.n_j = static_cast<int32_t>(by_cols ? h : n_c);
@@ -910,7 +979,9 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     ca.out_block_stride = static_cast<int64_t>(128) * pl.t_rpb * pl.ldt;
     // later groups travel during these launches: leave their token kernels somewhere to run
     b200::SmReserve room(last ? 0 : cm->sm_reserve);
-    if ((rc = b200tri_trimul_contract(&ca, stream_))) return rc;
+    log_launch(cm, B200TRI_CP_EVENT_CONTRACT, g, ca.n_i, ca.n_j, static_cast<const uint8_t*>(ca.a) - ws,
+               static_cast<const uint8_t*>(ca.b) - ws, static_cast<uint8_t*>(ca.out_bf16) - ws, ca.a_src_stride * 2);
+    if (!cm->dry && (rc = b200tri_trimul_contract(&ca, stream_))) return rc;
 
     // output stage of the same rows (or columns): it is local to a pair
     const int64_t row0 = by_cols ? 0 : static_cast<int64_t>(s) * n_c + static_cast<int64_t>(q) * h;
@@ -940,9 +1011,99 @@ extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args*
     fa.os_j = 128;
     fa.workspace = ws + pl.fin;
     fa.workspace_bytes = b200tri_trimul_finish_workspace_bytes();
-    if ((rc = b200tri_trimul_finish(&fa, stream_))) return rc;
+    log_launch(cm, B200TRI_CP_EVENT_OUTPUT, g, fa.n_i, fa.n_j, static_cast<const uint8_t*>(fa.t) - ws, 0, 0,
+               static_cast<uint8_t*>(fa.out) - static_cast<uint8_t*>(a->out));
+    if (!cm->dry && (rc = b200tri_trimul_finish(&fa, stream_))) return rc;
   }
   return B200TRI_OK;
+}
+
+// ---------------------------------------------------------------------------- dry run
+namespace {
+// a communicator that exists on the host only: grid coordinates, fake non-null workspaces
+void fake_comm(b200tri_comm* cm, int rows, int cols, int rank, int push, std::vector<b200tri_cp_event>* log) {
+  cm->world = rows * cols;
+  cm->rank = rank;
+  cm->rows = rows;
+  cm->cols = cols;
+  cm->m = cols / rows;
+  cm->r = rank / cols;
+  cm->c = rank % cols;
+  cm->push = push != 0;
+  cm->dry = log;
+  cm->ws = reinterpret_cast<void*>(static_cast<uintptr_t>(1) << 40);  // never dereferenced
+  cm->ws_bytes = static_cast<size_t>(1) << 46;
+  cm->peer_ws.assign(cm->world, cm->ws);
+}
+}  // namespace
+
+extern "C" int b200tri_cp_dry_run(int32_t rows, int32_t cols, int32_t rank, int32_t n, int32_t op, int32_t push,
+                                  b200tri_cp_event* out, int32_t capacity) {
+  if (b200::check_grid(rows * cols, rows, cols)) return -1;
+  if (rank < 0 || rank >= rows * cols || n <= 0 || n % cols || op < B200TRI_CP_TRIMUL_OUTGOING ||
+      op > B200TRI_CP_TRIATT_ENDING) {
+    b200::set_error("cp_dry_run: bad rank, token count or op");
+    return -1;
+  }
+  std::vector<b200tri_cp_event> log;
+  b200tri_comm cm;
+  fake_comm(&cm, rows, cols, rank, push, &log);
+  uint8_t* tile = reinterpret_cast<uint8_t*>(static_cast<uintptr_t>(1) << 50);  // stands for x and out; never dereferenced
+  int rc;
+  if (op <= B200TRI_CP_TRIMUL_INCOMING) {
+    b200tri_trimul_cp_args a = {};
+    a.n = n;
+    a.incoming = op == B200TRI_CP_TRIMUL_INCOMING;
+    a.eps = 1e-5f;
+    a.x = tile;
+    a.out = tile;
+    rc = b200tri_trimul_cp(&cm, &a, nullptr);
+  } else {
+    b200tri_triatt_cp_args a = {};
+    a.n = n;
+    a.starting = op == B200TRI_CP_TRIATT_STARTING;
+    a.heads = 4;
+    a.head_dim = 32;
+    a.eps = 1e-5f;
+    a.inf = 1e9f;
+    a.x = tile;
+    a.out = tile;
+    rc = b200tri_triatt_cp(&cm, &a, nullptr);
+  }
+  cm.peer_ws.clear();
+  cm.ws = nullptr;
+  if (rc) return -1;
+  if (out)
+    for (size_t i = 0; i < log.size() && static_cast<int32_t>(i) < capacity; ++i) out[i] = log[i];
+  return static_cast<int>(log.size());
+}
+
+extern "C" int b200tri_cp_layout(int32_t rows, int32_t cols, int32_t rank, int32_t n, int32_t op, int64_t* out) {
+  if (b200::check_grid(rows * cols, rows, cols)) return -1;
+  if (!out || rank < 0 || rank >= rows * cols || n <= 0 || n % cols || op < B200TRI_CP_TRIMUL_OUTGOING ||
+      op > B200TRI_CP_TRIATT_ENDING) {
+    b200::set_error("cp_layout: bad rank, token count, op or buffer");
+    return -1;
+  }
+  b200tri_comm cm;
+  fake_comm(&cm, rows, cols, rank, 1, nullptr);
+  cm.peer_ws.clear();
+  cm.ws = nullptr;
+  b200::TileDims d;
+  if (b200::tile_dims(&cm, n, &d)) return -1;
+  for (int i = 0; i < 16; ++i) out[i] = 0;
+  if (op <= B200TRI_CP_TRIMUL_INCOMING) {
+    const b200::TrimulPlan pl = b200::trimul_plan(&cm, d, op == B200TRI_CP_TRIMUL_INCOMING);
+    const int64_t v[8] = {(int64_t)pl.a_all, (int64_t)pl.a_loc, (int64_t)pl.b_all, (int64_t)pl.b_loc, (int64_t)pl.blk * 2,
+                          op == B200TRI_CP_TRIMUL_INCOMING ? 1 : cm.m, (int64_t)pl.t, (int64_t)pl.total};
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  } else {
+    const b200::TriattPlan pl = b200::triatt_plan(&cm, d, op == B200TRI_CP_TRIATT_STARTING);
+    const int64_t v[11] = {(int64_t)pl.q, (int64_t)pl.k_all, (int64_t)pl.vt_all, (int64_t)pl.bias_loc, (int64_t)pl.bias_all,
+                           (int64_t)pl.k_tile, (int64_t)pl.vt_tile, (int64_t)pl.bias_tile, pl.tiles, pl.own, (int64_t)pl.total};
+    for (int i = 0; i < 11; ++i) out[i] = v[i];
+  }
+  return 0;
 }
 
 // ---------------------------------------------------------------------------- tri-attn
@@ -1001,13 +1162,15 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   pa.bias_head_stride = static_cast<int64_t>(pl.n_outer) * pl.ld;
   pa.workspace = ws + pl.proj;
   pa.workspace_bytes = b200tri_triatt_project_workspace_bytes();
-  if ((rc = b200tri_triatt_project(&pa, stream_))) return rc;
+  log_launch(cm, B200TRI_CP_EVENT_PROJECT, -1, pa.n_outer, pa.n_inner, static_cast<uint8_t*>(pa.q) - ws,
+             static_cast<uint8_t*>(pa.k) - ws, static_cast<uint8_t*>(pa.vt) - ws, static_cast<uint8_t*>(pa.bias) - ws);
+  if (!cm->dry && (rc = b200tri_triatt_project(&pa, stream_))) return rc;
 
   // Two groups on the exchange stream: the bias chunks (small; even the own key tile's bias
   // may live on another rank) fence the first core launch, the peers' K/V tiles only the
   // second one, so they travel while the own key tile is computed.
-  B200_CUDA_OK(cudaEventRecord(cm->ev_ready, stream));
-  B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
+  CP_CUDA(cm, cudaEventRecord(cm->ev_ready, stream));
+  CP_CUDA(cm, cudaStreamWaitEvent(cm->stream, cm->ev_ready, 0));
   const std::vector<Msg> msgs =
       build_plan(Grid{cm->rows, cm->cols, m}, starting ? B200TRI_CP_TRIATT_STARTING : B200TRI_CP_TRIATT_ENDING);
   const size_t head_rows = static_cast<size_t>(pl.n_outer) * pl.ld * 2;  // one head of the sender's bias
@@ -1035,7 +1198,7 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
     }
   };
   if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
-  B200_CUDA_OK(cudaEventRecord(cm->ev_first, cm->stream));
+  CP_CUDA(cm, cudaEventRecord(cm->ev_first, cm->stream));
   // The peers' key tiles travel in groups of 1, 2, 4 tiles (in the order they are walked), each
   // fencing its own core launch: the first peer tile is computed while the next two arrive, and
   // so on, at the price of one spill of the running state per extra launch.
@@ -1050,7 +1213,7 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
     if ((rc = post_exchange(cm, ws, pull, msgs, [&](const Msg& x) { return x.what == WHAT_KV && group_of(x) == g; },
                             views, stream)))
       return rc;
-    B200_CUDA_OK(cudaEventRecord(g + 1 < n_groups ? cm->ev_part[g] : cm->ev_rest, cm->stream));
+    CP_CUDA(cm, cudaEventRecord(g + 1 < n_groups ? cm->ev_part[g] : cm->ev_rest, cm->stream));
   }
 
   // key tiles: the own one first, then the peers' in rotated order (every sender serves a
@@ -1090,31 +1253,41 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
     ca.workspace = ws + pl.core;
     ca.workspace_bytes = b200tri_triatt_core_multi_workspace_bytes(pl.n_outer, pl.n_inner, pl.tiles);
   }
-  B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_first, 0));
+  // dry-run log of one core launch: walk positions [lo, hi) of the key-tile order
+  auto log_core = [&](int launch, int lo, int hi) {
+    for (int idx = lo; idx < hi; ++idx)
+      log_launch(cm, B200TRI_CP_EVENT_CORE_TILE, launch, idx, (pl.own + idx) % pl.tiles,
+                 static_cast<const uint8_t*>(tiles[idx].k) - ws, static_cast<const uint8_t*>(tiles[idx].vt) - ws,
+                 static_cast<const uint8_t*>(tiles[idx].bias) - ws, 0);
+  };
+  CP_CUDA(cm, cudaStreamWaitEvent(stream, cm->ev_first, 0));
   tiles[0].unnormalized = pl.tiles > 1;
   {
     // the peers' key tiles travel during this launch: leave their token kernels somewhere to run
     b200::SmReserve room(pl.tiles > 1 ? cm->sm_reserve : 0);
-    if ((rc = b200tri_triatt_core(&tiles[0], stream_))) return rc;
+    log_core(0, 0, 1);
+    if (!cm->dry && (rc = b200tri_triatt_core(&tiles[0], stream_))) return rc;
   }
   if (pl.tiles > 1) {
     if (grouped) {
       for (int g = 0, lo = 1; g < n_groups; ++g) {
         const int hi = std::min(pl.tiles, 2 << g);  // walk positions [lo, hi)
         const bool last = g + 1 == n_groups;
-        B200_CUDA_OK(cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
+        CP_CUDA(cm, cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
         tiles[lo].resume = 1;
         tiles[lo].unnormalized = !last;
         b200::SmReserve room(last ? 0 : cm->sm_reserve);
-        if ((rc = b200tri_triatt_core_multi(&tiles[lo], hi - lo, stream_))) return rc;
+        log_core(g + 1, lo, hi);
+        if (!cm->dry && (rc = b200tri_triatt_core_multi(&tiles[lo], hi - lo, stream_))) return rc;
         lo = hi;
       }
     } else {  // ragged key tiles: one launch each, the state carried in acc_o
-      B200_CUDA_OK(cudaStreamWaitEvent(stream, cm->ev_rest, 0));
+      CP_CUDA(cm, cudaStreamWaitEvent(stream, cm->ev_rest, 0));
       for (int idx = 1; idx < pl.tiles; ++idx) {
         tiles[idx].resume = 1;
         tiles[idx].unnormalized = idx + 1 < pl.tiles;
-        if ((rc = b200tri_triatt_core(&tiles[idx], stream_))) return rc;
+        log_core(idx, idx, idx + 1);
+        if (!cm->dry && (rc = b200tri_triatt_core(&tiles[idx], stream_))) return rc;
       }
     }
   }
@@ -1137,5 +1310,6 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   fa.os_inner = xs_i;
   fa.workspace = ws + pl.fin;
   fa.workspace_bytes = b200tri_triatt_finish_workspace_bytes();
+  if (cm->dry) return B200TRI_OK;
   return b200tri_triatt_finish(&fa, stream_);
 }

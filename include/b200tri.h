@@ -471,6 +471,30 @@ int b200tri_cp_plan(int32_t rows, int32_t cols, int32_t op, b200tri_cp_msg* out,
  * the reference, whose ring hops are scheduled by XLA. */
 int b200tri_cp_rounds(int32_t rows, int32_t cols, int32_t op, int32_t what, int32_t* round, int32_t capacity);
 
+/* Dry run of one context-parallel op, for checks on a machine without a GPU: what rank `rank`
+ * of a rows x cols grid would do for `op` at n tokens - every copy it issues (the tiles it
+ * writes into its peers' workspaces with push = 1, the ones it reads out of them with push = 0,
+ * its local copies) and every launch it makes - without a CUDA or NCCL call. Offsets are bytes
+ * from the start of a rank's exchange workspace (src_off in the sender's, dst_off in the
+ * receiver's; off[0..2] of a launch in the rank's own) or from the start of its tile (off[3] of
+ * an output stage). `group` numbers the exchange groups (and the launches they fence), `round`
+ * the copy rounds inside a group. Returns the number of events (at most `capacity` are written),
+ * or -1. b200tri_cp_layout gives the byte offsets of the arrays in the workspace:
+ * tri-mult: {a slots, own a, b slots, own b, bytes of one block, blocks per a slot, t, total};
+ * tri-attn: {q, k slots, vT slots, own bias, bias slots, bytes of a k tile, of a vT tile, of a
+ * bias tile, key tiles, own tile index, total}. No counterpart in the reference (XLA schedules
+ * its collective-permutes). */
+enum { B200TRI_CP_EVENT_LOCAL_COPY = 0, B200TRI_CP_EVENT_COPY = 1, B200TRI_CP_EVENT_PROJECT = 2,
+       B200TRI_CP_EVENT_CONTRACT = 3, B200TRI_CP_EVENT_OUTPUT = 4, B200TRI_CP_EVENT_CORE_TILE = 5 };
+typedef struct {
+  int32_t kind, group, round, src, dst, what, block, slot0, slot1, n_i, n_j, reserved;
+  int64_t src_off, dst_off, bytes;
+  int64_t off[4];
+} b200tri_cp_event;
+int b200tri_cp_dry_run(int32_t rows, int32_t cols, int32_t rank, int32_t n, int32_t op, int32_t push,
+                       b200tri_cp_event* out, int32_t capacity);
+int b200tri_cp_layout(int32_t rows, int32_t cols, int32_t rank, int32_t n, int32_t op, int64_t* out16);
+
 /* Triangle multiplication on this rank's tile. x / residual / out are the rank's tile
  * [n / rows][n / cols][128] bf16; mask is the WHOLE [n][n] float32 mask (or NULL), replicated
  * on every rank; parameters as in b200tri_trimul_args. n must be a multiple of cols (pad

@@ -54,7 +54,7 @@ def test_struct_sizes_match_the_header():
         pytest.skip("gcc not available")
     names = dict(_lib.STRUCTS)
     header = (ROOT / "include" / "b200tri.h").read_text()
-    assert set(re.findall(r"}\s*(b200tri_[a-z_]+_(?:args|msg));", header)) == set(names)
+    assert set(re.findall(r"}\s*(b200tri_[a-z_]+_(?:args|msg|event));", header)) == set(names)
     assert set(re.findall(r"}\s*(b200tri_[a-z_]+_params);", header)) == set(_lib.PARAM_STRUCTS)
     names.update(_lib.PARAM_STRUCTS)
     src = '#include <stdio.h>\n#include "b200tri.h"\nint main(void){\n'
