@@ -51,8 +51,6 @@ struct b200tri_comm {
   // and the launches it would make are written to this log instead, for checks on a CPU.
   std::vector<b200tri_cp_event>* dry = nullptr;
   int dry_group = 0;
-  // (sender, receiver) pairs that have exchanged their opening token in the op under way
-  std::vector<char> opened;
   cudaStream_t copy_stream[4] = {nullptr, nullptr, nullptr, nullptr};  // [0] is `stream`
   cudaEvent_t ev_fork = nullptr, ev_join[4] = {nullptr, nullptr, nullptr, nullptr};
 };
@@ -251,43 +249,51 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
   auto remote = [&](const Msg& msg) {
     return want(msg) && msg.src != msg.dst && (msg.src == cm->rank || msg.dst == cm->rank);
   };
-  const bool dry = cm->dry != nullptr;
-  const int group = dry ? cm->dry_group++ : 0;
-  // dry run: one log entry per piece of a message
-  auto log_copy = [&](const Msg& msg, int kind, int rnd) {
-    send.clear();
-    recv.clear();
-    views(msg, true, msg.src, send);
-    views(msg, false, msg.dst, recv);
-    for (size_t i = 0; i < send.size(); ++i) {
-      b200tri_cp_event e = {};
-      e.kind = kind;
-      e.group = group;
-      e.round = rnd;
-      e.src = msg.src;
-      e.dst = msg.dst;
-      e.what = msg.what;
-      e.block = msg.block;
-      e.slot0 = msg.slot0;
-      e.slot1 = msg.slot1;
-      e.src_off = static_cast<int64_t>(send[i].off);
-      e.dst_off = static_cast<int64_t>(recv[i].off);
-      e.bytes = static_cast<int64_t>(send[i].bytes);
-      cm->dry->push_back(e);
-    }
-  };
-  const Nccl* api = dry ? nullptr : nccl_api();
-  B200_REQUIRE(dry || api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
+  if (cm->dry) {
+    // the copies this rank would issue, in issue order: local ones, then the remote ones it
+    // sends (push) or fetches (pull) round by round
+    const int group = cm->dry_group++;
+    const std::vector<int> round = copy_rounds(msgs, cm->world, want, big);
+    int n_rounds = 0;
+    for (int r : round) n_rounds = std::max(n_rounds, r + 1);
+    auto log = [&](const Msg& msg, int kind, int rnd) {
+      send.clear();
+      recv.clear();
+      views(msg, true, msg.src, send);
+      views(msg, false, msg.dst, recv);
+      for (size_t i = 0; i < send.size(); ++i) {
+        b200tri_cp_event e = {};
+        e.kind = kind;
+        e.group = group;
+        e.round = rnd;
+        e.src = msg.src;
+        e.dst = msg.dst;
+        e.what = msg.what;
+        e.block = msg.block;
+        e.slot0 = msg.slot0;
+        e.slot1 = msg.slot1;
+        e.src_off = static_cast<int64_t>(send[i].off);
+        e.dst_off = static_cast<int64_t>(recv[i].off);
+        e.bytes = static_cast<int64_t>(send[i].bytes);
+        cm->dry->push_back(e);
+      }
+    };
+    for (const Msg& msg : msgs)
+      if (want(msg) && msg.src == cm->rank && msg.dst == cm->rank) log(msg, B200TRI_CP_EVENT_LOCAL_COPY, -1);
+    for (int r = 0; r < n_rounds; ++r)
+      for (size_t i = 0; i < msgs.size(); ++i)
+        if (round[i] == r && (pull ? (cm->push ? msgs[i].src : msgs[i].dst) : msgs[i].src) == cm->rank)
+          log(msgs[i], B200TRI_CP_EVENT_COPY, r);
+    return B200TRI_OK;
+  }
+  const Nccl* api = nccl_api();
+  B200_REQUIRE(api != nullptr, B200TRI_ERR_CUDA, "libnccl.so.2 could not be loaded");
   // with timing on, the span of this exchange on the exchange stream (it starts when the stream
   // has seen the caller's "tiles are ready" event, so it is transfer time plus peer skew)
-  TimedLaunch timed(K_CP_EXCHANGE, cm->stream, !dry);
+  TimedLaunch timed(K_CP_EXCHANGE, cm->stream);
   // local messages
   for (const Msg& msg : msgs) {
     if (!want(msg) || msg.src != cm->rank || msg.dst != cm->rank) continue;
-    if (dry) {
-      log_copy(msg, B200TRI_CP_EVENT_LOCAL_COPY, -1);
-      continue;
-    }
     send.clear();
     recv.clear();
     views(msg, true, cm->rank, send);
@@ -298,13 +304,8 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
   }
   bool any = false;
   for (const Msg& msg : msgs) any = any || remote(msg);
+  if (!any) return B200TRI_OK;
   if (!pull) {
-    if (!any) return B200TRI_OK;
-    if (dry) {
-      for (const Msg& msg : msgs)
-        if (remote(msg) && msg.src == cm->rank) log_copy(msg, B200TRI_CP_EVENT_COPY, 0);
-      return B200TRI_OK;
-    }
     B200_NCCL_OK(api, api->GroupStart());
     for (const Msg& msg : msgs) {
       if (!remote(msg)) continue;
@@ -318,112 +319,78 @@ int post_exchange(b200tri_comm* cm, uint8_t* ws, bool pull, const std::vector<Ms
     B200_NCCL_OK(api, api->GroupEnd());
     return B200TRI_OK;
   }
-  // Tokens: 4 bytes through NCCL, one per (sender, receiver) pair of the group. Slot 0 of the
-  // token buffer is what this rank sends, slot 1 + peer what it receives from that peer.
-  // to_receiver = true: from a message's sender to its receiver; false: the reverse. An OPENING
-  // token says "this rank has reached the op" (push: the receiver's slots are no longer read by
-  // its earlier work; pull: the sender's tiles are complete), which stays true for the rest of
-  // the op: every pair of the op exchanges it once, in the op's first exchange (cm->opened,
-  // cleared when an op begins; both sides walk the same messages in the same order, so they
-  // agree on which tokens exist).
-  auto token_round = [&](bool to_receiver, bool opening) -> int {
-    std::vector<std::pair<int, bool>> ops;  // (peer, this rank sends)
-    std::vector<char> in_round(static_cast<size_t>(cm->world) * cm->world, 0);
-    for (const Msg& msg : msgs) {
-      // the opening tokens of ALL pairs of the op travel in its first exchange, whichever group
-      // their tiles belong to; closing tokens belong to the group of the tiles
-      if (opening ? (msg.src == msg.dst || (msg.src != cm->rank && msg.dst != cm->rank)) : !remote(msg)) continue;
-      const size_t key = static_cast<size_t>(msg.src) * cm->world + msg.dst;
-      if (in_round[key]) continue;
-      in_round[key] = 1;
-      if (opening) {
-        if (cm->opened[key]) continue;
-        cm->opened[key] = 1;
-      }
-      const bool i_send = to_receiver ? msg.src == cm->rank : msg.dst == cm->rank;
-      ops.emplace_back(msg.src == cm->rank ? msg.dst : msg.src, i_send);
-    }
-    if (ops.empty()) return B200TRI_OK;
-    if (dry) {
-      for (const auto& op : ops) {
-        b200tri_cp_event e = {};
-        e.kind = op.second ? B200TRI_CP_EVENT_TOKEN_SEND : B200TRI_CP_EVENT_TOKEN_RECV;
-        e.group = group;
-        e.round = opening ? 0 : 1;
-        e.src = op.second ? cm->rank : op.first;  // the token's sender
-        e.dst = op.second ? op.first : cm->rank;
-        e.what = e.block = e.slot0 = e.slot1 = -1;
-        cm->dry->push_back(e);
-      }
-      return B200TRI_OK;
-    }
+  // tokens: slot 0 is what this rank sends, slot 1 + peer what it receives from that peer.
+  // to_receiver = true: one token per message from its sender to its receiver; false: the reverse.
+  auto token_round = [&](bool to_receiver) -> int {
     B200_NCCL_OK(api, api->GroupStart());
-    for (const auto& op : ops) {
-      if (op.second)
-        B200_NCCL_OK(api, api->Send(cm->tokens, 4, ncclUint8, op.first, cm->nccl, cm->stream));
+    for (const Msg& msg : msgs) {
+      if (!remote(msg)) continue;
+      const bool i_send = to_receiver ? msg.src == cm->rank : msg.dst == cm->rank;
+      const int peer = msg.src == cm->rank ? msg.dst : msg.src;
+      if (i_send)
+        B200_NCCL_OK(api, api->Send(cm->tokens, 4, ncclUint8, peer, cm->nccl, cm->stream));
       else
-        B200_NCCL_OK(api, api->Recv(cm->tokens + 64 * (1 + op.first), 4, ncclUint8, op.first, cm->nccl, cm->stream));
+        B200_NCCL_OK(api, api->Recv(cm->tokens + 64 * (1 + peer), 4, ncclUint8, peer, cm->nccl, cm->stream));
     }
     B200_NCCL_OK(api, api->GroupEnd());
     return B200TRI_OK;
   };
   const bool push = cm->push;
-  if (cm->opened.size() != static_cast<size_t>(cm->world) * cm->world) cm->opened.assign(static_cast<size_t>(cm->world) * cm->world, 0);
   int rc;
   {
     // with timing on: how long the peers were waited for
-    TimedLaunch waited(K_CP_READY, cm->stream, !dry);
-    // pull: every sender's tiles are complete. push: every receiver has reached this op,
+    TimedLaunch waited(K_CP_READY, cm->stream);
+    // pull: every sender's tiles are complete. push: every receiver has reached this exchange,
     // so nothing of its earlier work still reads the slots about to be written.
-    rc = token_round(!push, true);
+    rc = token_round(!push);
   }
   if (rc) return rc;
-  if (!any) return B200TRI_OK;  // nothing of this group concerns this rank
-  TimedLaunch copied(K_CP_COPY, cm->stream, !dry);  // ... and the copies themselves (plus the closing round)
-  if (!dry && cm->n_copy > 1) {
+  TimedLaunch copied(K_CP_COPY, cm->stream);  // ... and the copies themselves (plus the closing round)
+  if (cm->n_copy > 1) {
     B200_CUDA_OK(cudaEventRecord(cm->ev_fork, cm->stream));
     for (int i = 1; i < cm->n_copy; ++i) B200_CUDA_OK(cudaStreamWaitEvent(cm->copy_stream[i], cm->ev_fork, 0));
   }
   // Order of the copies: rounds in which every rank sends at most one tile and receives at most
-  // one (an edge colouring of the whole exchange, the same on every rank). Taken in plan order
-  // instead, several senders serve the same receiver at the same time while other receivers
-  // wait, and the exchange runs at half the link rate.
-  const std::vector<int> round = copy_rounds(msgs, cm->world, want, big);
-  int n_rounds = 0;
-  for (int r : round) n_rounds = std::max(n_rounds, r + 1);
-  for (int r = 0; r < n_rounds; ++r)
-    for (size_t idx = 0; idx < msgs.size(); ++idx) {
-      const Msg& msg = msgs[idx];
-      if (round[idx] != r || (push ? msg.src : msg.dst) != cm->rank) continue;
-      if (dry) {
-        log_copy(msg, B200TRI_CP_EVENT_COPY, r);
-        continue;
-      }
-      send.clear();
-      recv.clear();
-      views(msg, true, msg.src, send);
-      views(msg, false, msg.dst, recv);
-      const int peer = push ? msg.dst : msg.src;
-      uint8_t* theirs = static_cast<uint8_t*>(cm->peer_ws[peer]);
-      for (size_t i = 0; i < send.size(); ++i) {
-        const uint8_t* from = push ? ws + send[i].off : theirs + send[i].off;
-        uint8_t* to = push ? theirs + recv[i].off : ws + recv[i].off;
-        // every piece is cut into n_copy parts, one per stream
-        const size_t part = (send[i].bytes / cm->n_copy + 1023) / 1024 * 1024;
-        for (int k = 0; k < cm->n_copy; ++k) {
-          const size_t lo = std::min(send[i].bytes, part * k), hi = std::min(send[i].bytes, part * (k + 1));
-          if (hi > lo)
-            B200_CUDA_OK(cudaMemcpyAsync(to + lo, from + lo, hi - lo, cudaMemcpyDeviceToDevice, cm->copy_stream[k]));
-        }
+  // one (a greedy edge colouring of the whole exchange, the same on every rank, busiest ranks
+  // first). Taken in plan order instead, several senders serve the same receiver at the same
+  // time while other receivers wait, and the exchange runs at half the link rate.
+  std::vector<int> order;  // indices into msgs of the copies this rank issues, round by round
+  {
+    const std::vector<int> round = copy_rounds(msgs, cm->world, want, big);
+    int n_rounds = 0;
+    for (int r : round) n_rounds = std::max(n_rounds, r + 1);
+    for (int r = 0; r < n_rounds; ++r)
+      for (size_t i = 0; i < msgs.size(); ++i)
+        if (round[i] == r && (push ? msgs[i].src : msgs[i].dst) == cm->rank) order.push_back(static_cast<int>(i));
+  }
+  for (int idx : order) {
+    const Msg& msg = msgs[idx];
+    send.clear();
+    recv.clear();
+    views(msg, true, msg.src, send);
+    views(msg, false, msg.dst, recv);
+    const int peer = push ? msg.dst : msg.src;
+    uint8_t* theirs = static_cast<uint8_t*>(cm->peer_ws[peer]);
+    for (size_t i = 0; i < send.size(); ++i) {
+      const uint8_t* from = push ? ws + send[i].off : theirs + send[i].off;
+      uint8_t* to = push ? theirs + recv[i].off : ws + recv[i].off;
+      // every piece is cut into n_copy parts, one per stream: two copy engines working on one
+      // tile come closer to the link rate than one
+      const size_t part = (send[i].bytes / cm->n_copy + 1023) / 1024 * 1024;
+      for (int k = 0; k < cm->n_copy; ++k) {
+        const size_t lo = std::min(send[i].bytes, part * k), hi = std::min(send[i].bytes, part * (k + 1));
+        if (hi > lo)
+          B200_CUDA_OK(cudaMemcpyAsync(to + lo, from + lo, hi - lo, cudaMemcpyDeviceToDevice, cm->copy_stream[k]));
       }
     }
-  for (int i = 1; !dry && i < cm->n_copy; ++i) {
+  }
+  for (int i = 1; i < cm->n_copy; ++i) {
     B200_CUDA_OK(cudaEventRecord(cm->ev_join[i], cm->copy_stream[i]));
     B200_CUDA_OK(cudaStreamWaitEvent(cm->stream, cm->ev_join[i], 0));
   }
   // pull: every tile has been read, the senders may reuse their buffers. push: every tile has
   // been written (the sender's own buffers are protected by its stream order).
-  return token_round(push, false);
+  return token_round(push);
 }
 
 // CUDA calls of the ops that a dry run skips
@@ -858,7 +825,6 @@ extern "C" size_t b200tri_trimul_cp_workspace_bytes(const b200tri_comm* cm, int3
 extern "C" int b200tri_trimul_cp(b200tri_comm* cm, const b200tri_trimul_cp_args* a, b200tri_stream_t stream_) {
   int rc = check_comm(cm, "trimul_cp");
   if (rc) return rc;
-  cm->opened.assign(static_cast<size_t>(cm->world) * cm->world, 0);  // a new op: no pair has exchanged its opening token
   B200_REQUIRE(a != nullptr && a->x && a->out, B200TRI_ERR_INVALID, "trimul_cp: null args, x or out");
   TileDims d;
   if ((rc = tile_dims(cm, a->n, &d))) return rc;
@@ -1152,7 +1118,6 @@ extern "C" size_t b200tri_triatt_cp_workspace_bytes(const b200tri_comm* cm, int3
 extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args* a, b200tri_stream_t stream_) {
   int rc = check_comm(cm, "triatt_cp");
   if (rc) return rc;
-  cm->opened.assign(static_cast<size_t>(cm->world) * cm->world, 0);  // a new op: no pair has exchanged its opening token
   B200_REQUIRE(a != nullptr && a->x && a->out, B200TRI_ERR_INVALID, "triatt_cp: null args, x or out");
   B200_REQUIRE(a->heads == 4 && a->head_dim == 32, B200TRI_ERR_UNSUPPORTED,
                "triatt_cp: built for 4 heads x 32 (got %d x %d)", a->heads, a->head_dim);
@@ -1234,16 +1199,16 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   };
   if ((rc = post_exchange(cm, ws, pull, msgs, [](const Msg& x) { return x.what == WHAT_BIAS; }, views, stream))) return rc;
   CP_CUDA(cm, cudaEventRecord(cm->ev_first, cm->stream));
-  // The peers' key tiles travel one per group, in the order they are walked, each fencing its own
-  // core launch: a tile is computed while the next one arrives (on one box a tile takes about as
-  // long to fetch as to compute), at the price of one spill of the running state per launch.
+  // The peers' key tiles travel in groups of 1, 2, 4 tiles (in the order they are walked), each
+  // fencing its own core launch: the first peer tile is computed while the next two arrive, and
+  // so on, at the price of one spill of the running state per extra launch.
   const bool grouped = pl.n_inner % 64 == 0;
   auto group_of = [&](const Msg& msg) {  // of a K/V message, seen from its receiver
     const int own = starting ? msg.dst % cm->cols : msg.dst / cm->cols;
     const int idx = (msg.slot0 - own + pl.tiles) % pl.tiles;  // position in the receiver's walk (>= 1)
-    return grouped && idx > 1 ? idx - 1 : 0;  // (the own tile, idx 0, is a local message onto itself)
+    return !grouped ? 0 : idx < 2 ? 0 : idx < 4 ? 1 : 2;
   };
-  const int n_groups = grouped && pl.tiles > 1 ? pl.tiles - 1 : 1;
+  const int n_groups = !grouped || pl.tiles <= 2 ? 1 : pl.tiles <= 4 ? 2 : 3;
   for (int g = 0; g < n_groups; ++g) {
     if ((rc = post_exchange(cm, ws, pull, msgs, [&](const Msg& x) { return x.what == WHAT_KV && group_of(x) == g; },
                             views, stream)))
@@ -1306,7 +1271,7 @@ extern "C" int b200tri_triatt_cp(b200tri_comm* cm, const b200tri_triatt_cp_args*
   if (pl.tiles > 1) {
     if (grouped) {
       for (int g = 0, lo = 1; g < n_groups; ++g) {
-        const int hi = lo + 1;  // walk positions [lo, hi): one tile per group
+        const int hi = std::min(pl.tiles, 2 << g);  // walk positions [lo, hi)
         const bool last = g + 1 == n_groups;
         CP_CUDA(cm, cudaStreamWaitEvent(stream, last ? cm->ev_rest : cm->ev_part[g], 0));
         tiles[lo].resume = 1;

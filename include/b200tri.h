@@ -478,16 +478,14 @@ int b200tri_cp_rounds(int32_t rows, int32_t cols, int32_t op, int32_t what, int3
  * from the start of a rank's exchange workspace (src_off in the sender's, dst_off in the
  * receiver's; off[0..2] of a launch in the rank's own) or from the start of its tile (off[3] of
  * an output stage). `group` numbers the exchange groups (and the launches they fence), `round`
- * the copy rounds inside a group; a token event is one 4-byte token from `src` to `dst`, sent
- * or expected by this rank, in the opening (round 0) or closing (round 1) exchange of a group. Returns the number of events (at most `capacity` are written),
+ * the copy rounds inside a group. Returns the number of events (at most `capacity` are written),
  * or -1. b200tri_cp_layout gives the byte offsets of the arrays in the workspace:
  * tri-mult: {a slots, own a, b slots, own b, bytes of one block, blocks per a slot, t, total};
  * tri-attn: {q, k slots, vT slots, own bias, bias slots, bytes of a k tile, of a vT tile, of a
  * bias tile, key tiles, own tile index, total}. No counterpart in the reference (XLA schedules
  * its collective-permutes). */
 enum { B200TRI_CP_EVENT_LOCAL_COPY = 0, B200TRI_CP_EVENT_COPY = 1, B200TRI_CP_EVENT_PROJECT = 2,
-       B200TRI_CP_EVENT_CONTRACT = 3, B200TRI_CP_EVENT_OUTPUT = 4, B200TRI_CP_EVENT_CORE_TILE = 5,
-       B200TRI_CP_EVENT_TOKEN_SEND = 6, B200TRI_CP_EVENT_TOKEN_RECV = 7 };
+       B200TRI_CP_EVENT_CONTRACT = 3, B200TRI_CP_EVENT_OUTPUT = 4, B200TRI_CP_EVENT_CORE_TILE = 5 };
 typedef struct {
   int32_t kind, group, round, src, dst, what, block, slot0, slot1, n_i, n_j, reserved;
   int64_t src_off, dst_off, bytes;

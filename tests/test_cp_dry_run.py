@@ -26,7 +26,7 @@ from foldjax_b200 import _lib
 from foldjax_b200.cp_plan import Grid
 
 GRIDS = [(1, 2), (2, 2), (2, 4), (1, 4), (3, 3), (2, 6), (4, 4)]
-LOCAL, COPY, PROJECT, CONTRACT, OUTPUT, CORE_TILE, TOKEN_SEND, TOKEN_RECV = range(8)
+LOCAL, COPY, PROJECT, CONTRACT, OUTPUT, CORE_TILE = range(6)
 
 
 def _events(rows, cols, rank, n, op, push):
@@ -211,48 +211,6 @@ def test_triatt_exchange_and_tile_walk(rows, cols, n_c, push):
                         assert 1 <= group <= e.group, (rows, cols, dst, op, t, group, e.group)
                     elif e.off[2] <= dst_off < e.off[2] + bias_tile:
                         assert group == 0
-
-
-@pytest.mark.parametrize("push", [1, 0])
-@pytest.mark.parametrize("rows,cols", GRIDS)
-def test_tokens_pair_up_and_fence_every_copy(rows, cols, push):
-    """The 4-byte tokens around the copies: every token one rank sends is expected by the rank it
-    goes to, in the same exchange of the same group (an unmatched send or receive would hang
-    NCCL); every tile is preceded by an opening token between its two ranks somewhere earlier in
-    the op (push: the receiver's "my slots are free"; pull: the sender's "my tiles are ready") and
-    followed by a closing token in its own group (push: "written"; pull: "consumed")."""
-    grid = Grid(rows, cols)
-    for n_c in (128, 256, 512):
-        for op in range(4):
-            n = cols * n_c
-            events = {rank: _events(rows, cols, rank, n, op, push) for rank in grid.ranks()}
-            sends, recvs = {}, {}
-            for rank, evs in events.items():
-                for e in evs:
-                    if e.kind == TOKEN_SEND:
-                        assert e.src == rank
-                        sends.setdefault((e.group, e.round), []).append((e.src, e.dst))
-                    elif e.kind == TOKEN_RECV:
-                        assert e.dst == rank
-                        recvs.setdefault((e.group, e.round), []).append((e.src, e.dst))
-            assert sends.keys() == recvs.keys()
-            for key in sends:
-                assert sorted(sends[key]) == sorted(recvs[key]), (rows, cols, op, key)
-                assert len(set(sends[key])) == len(sends[key])  # one token per pair and exchange
-            opened = {}
-            for (group, rnd), pairs in sorted(sends.items()):
-                if rnd == 0:
-                    for pair in pairs:
-                        assert pair not in opened, "an opening token is sent once per pair and op"
-                        opened[pair] = group
-            for evs in events.values():
-                for e in evs:
-                    if e.kind != COPY:
-                        continue
-                    opening = (e.dst, e.src) if push else (e.src, e.dst)
-                    closing = (e.src, e.dst) if push else (e.dst, e.src)
-                    assert opened.get(opening, 1 << 30) <= e.group, (rows, cols, op, e.src, e.dst, e.group)
-                    assert closing in sends.get((e.group, 1), []), (rows, cols, op, e.src, e.dst, e.group)
 
 
 def test_dry_run_refuses_what_the_ops_refuse():
