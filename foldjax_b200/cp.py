@@ -1,9 +1,10 @@
 """2-D context-parallel triangle ops - host side.
 
 The data plane lives in libb200tri: ``b200tri_comm_*`` (a communicator over NCCL) and
-``b200tri_trimul_cp`` / ``b200tri_triatt_cp`` (the two triangle ops on one rank's tile,
-tiles exchanged over NVLink with grouped ncclSend/ncclRecv on the communicator's own
-stream, event-fenced, enqueue-only). This module is the thin Python caller: it keeps the
+``b200tri_trimul_cp`` / ``b200tri_triatt_cp`` (the two triangle ops on one rank's tile;
+tiles cross NVLink on the communicator's own stream, event-fenced and enqueue-only: written
+by the copy engines into the peers' CUDA-IPC-mapped workspaces with NCCL carrying 4-byte
+tokens, or as grouped ncclSend/ncclRecv - see ``TRANSPORT`` below). This module is the thin Python caller: it keeps the
 reference's option surface - ``context_parallel(cp_devices, layout=)``
 (src/foldjax/models/_cp.py:259) and the ``cp_devices`` / ``cp_layout`` knobs - creates
 the communicator (the 128-byte NCCL id travels over ``torch.distributed``, which is used

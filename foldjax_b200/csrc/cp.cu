@@ -6,8 +6,11 @@
 // ring_triangle_attention_2d, src/foldjax/models/_cp_attention.py:197-403. The reference
 // runs inside shard_map on a square device grid and moves tiles with skews and ring hops;
 // here the grid is R x C with C = m * R (1x2, 2x2, 2x4 on one 8-GPU box) and every tile
-// is fetched straight from its owner with grouped ncclSend/ncclRecv: NVSwitch gives every
-// pair of GPUs the same bandwidth, so a rotated direct fetch replaces skew + hops.
+// travels straight between its owner and the rank that needs it: NVSwitch gives every pair of
+// GPUs the same bandwidth, so a direct transfer replaces skew + hops. With one process per GPU
+// the copy engines write the tiles into the receivers' CUDA-IPC-mapped workspaces (or the
+// receivers read them) and NCCL only carries 4-byte tokens; otherwise the tiles are grouped
+// ncclSend/ncclRecv (post_exchange below).
 //
 // Everything is enqueue-only. The exchange runs on the communicator's own stream and is
 // fenced against the caller's stream with events in both directions, so the host never
