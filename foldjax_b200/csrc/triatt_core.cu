@@ -14,21 +14,28 @@
 // step, so the bias (the only operand that does not depend on i) crosses
 // L2 -> shared memory once per NWG rows.
 //
-//   warp 0        (warps 0-3 form the control warpgroup; 2 and 3 idle) TMA producer: Q tiles per item; per 64-key step the bias tile and,
-//                 per row, K [64x32], V^T [32x64] and the mask-bias row
-//   warp 1        Q.K^T issuer: S = Q K^T (bf16, 128x64x32) into TMEM
-//   warp 2        P.V issuer: O += P V (fp16, 128x32x64) with P read from TMEM
-//   warpgroups    softmax: one thread per query row. S from TMEM, + bias + mask,
-//                 running max with lazy rescale (the subtracted offset only moves
-//                 when the max grew by more than 2^8, so O stays in TMEM and is
-//                 rescaled rarely), exp2, row sum, P -> fp16 -> TMEM
+//   warp 0        (warps 0-3 form the control warpgroup; warp 3 idle) TMA producer: Q tiles per
+//                 item; per 64-key step the bias tile and, per row, K [64x32], V^T [32x64] and
+//                 the mask-bias row
+//   warp 1        score issuer: S = bias . I + Q K^T into TMEM. The bias tile of the step is a
+//                 K-major A operand itself; times a 64 x 64 identity it lands in the accumulator
+//                 exactly, so the softmax threads never touch it (bf16, 128x64, 4 + 2 MMAs)
+//   warp 2        P.V issuer: O += P V (fp16, 128x48x64) with P read from TMEM
+//   warpgroups    softmax: one thread per query row. S from TMEM (+ the mask row where the step
+//                 has dropped or soft-masked keys), running max with lazy rescale (the offset is
+//                 an integer in log2 units and only moves when the max grew by more than 2^8,
+//                 so O stays in TMEM, is rescaled rarely and by exact powers of two), the
+//                 exponentials split between the MUFU unit and a cubic on the FMA pipe,
+//                 P -> fp16 -> TMEM
 // TMEM per warpgroup: S 64 columns, P 32 (fp16 pairs), O 32 + the row sum (column 128 of
 // the group; rows 32..47 of every V tile are a row of ones and zero padding, so the
-// tensor core accumulates sum_k P next to P.V).
+// tensor core accumulates sum_k P next to P.V). Registers are moved from the control warpgroup
+// to the softmax warpgroups at start-up (setmaxnreg).
 //
-// Bound: not the tensor pipe. Per score the SM issues ~8 ALU/MUFU instructions
-// (unpack bias, packed add, 3-input max, packed fma, ex2, packed sum, half a cvt) against 128 tensor flops; at
-// 128 lanes/clk/SM that caps the tensor pipe near 25-30 % at head dim 32.
+// Bound: not the tensor pipe and not HBM. Per score the SM issues about 7 instructions (3-input
+// max, packed fma, ex2 or the cubic with its exponent insertion, clamp, half a cvt) against 128
+// tensor flops, and the MUFU unit delivers 16 exponentials per clock and SM: the kernel runs
+// at about 60 % of its issue slots with the tensor pipe under 40 % busy at head dim 32.
 #include <cuda_fp16.h>
 
 #include <mutex>

@@ -14,7 +14,7 @@
 //   warp 1      MMA issuer: D1 = LN_in(x) . g_out^T, D2 = LN_out(t) . p_out^T
 //   warps 2-5   layer norms, one thread per pair; the t tile is transposed into
 //               operand layout in place (read column, mbarrier, write row)
-//   warps 6-9   epilogue: D2 * sigmoid(D1) (+ residual) -> bf16 -> global
+//   warps 6-9   epilogue: D2 * sigmoid(D1) (+ residual) -> bf16 -> shared-memory tile -> TMA store
 // TMEM: 2 x (D1, D2) so the epilogue overlaps the next tile's MMAs.
 //
 // Bound: HBM (read t and x, write out: 3 * n_i*n_j*128*2 bytes; + residual).
