@@ -72,3 +72,12 @@ def test_streamed_blocks_refuse_mismatched_host_buffers():
         stream_host_blocks(run, [(z, None)], [z.clone(), z.clone()])
     with pytest.raises(ValueError, match="outputs must be"):
         stream_host_blocks(run, [(z, None)], [z.float()])
+
+
+def test_block_variant_names_are_checked_before_any_device_work():
+    from foldjax_b200.pairformer import VARIANTS, pairformer_forward
+
+    assert set(VARIANTS) == {"boltz2", "protenix", "openfold3"}
+    z = torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="Unsupported pairformer variant"):
+        pairformer_forward([{}], None, z, None, None, variant="alphafold2")
